@@ -1,0 +1,115 @@
+/*
+ * crispybits_b200.h -- C ABI of the B200 (sm_100a) packed W2/W3/W4 linear path.
+ *
+ * This shared library (libcrispybits_b200.so) replaces the reference's pybind11 binding file
+ * Crispybits/Kernel/csrc/bindings.cpp:32-40 and the libtorch-typed launchers behind it.  Every
+ * entry point takes raw device pointers, sizes and a CUDA stream; nothing here depends on torch.
+ *
+ * Conventions
+ *   - All pointers are device pointers on the CURRENT CUDA device unless stated otherwise.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).  Calls are
+ *     asynchronous: they return after enqueueing work.
+ *   - Return value: CB_OK (0) or a CB_ERR_* code; cb_last_error() gives the message of the last
+ *     failing call on the calling thread.
+ *   - dtype: element type of x, scales, zeros, bias and of the outputs (they must agree, as in
+ *     Crispybits/Kernel/csrc/host_utils.h:58,84): CB_F32, CB_F16 or CB_BF16.
+ *   - Weight format (Crispybits/Kernel/crispybits_kernels/reference.py:37-55,70-76): `packed` is
+ *     int32 [n, ceil(K/32)*bits], a per-row little-endian bitstream with code k at bit k*bits,
+ *     rows padded with zero codes to a multiple of 32 codes; `scales` / `zeros` are [n, ceil(K/group_size)]
+ *     in `dtype`; `bias` is [n] in `dtype` or NULL.
+ *   - Scratch: the decode kernels need device scratch when split_k > 1 (partial sums and
+ *     per-tile arrival counters).  The caller owns it: size it with cb_gemv_scratch_bytes(), zero
+ *     it ONCE after allocation, and pass it to every call; the kernels leave the counter region
+ *     zero again when they finish.  Two calls that may overlap on the GPU (different streams)
+ *     need different scratch buffers.
+ */
+#ifndef CRISPYBITS_B200_H
+#define CRISPYBITS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { CB_OK = 0, CB_ERR_INVALID = 1, CB_ERR_CUDA = 2, CB_ERR_UNSUPPORTED = 3 };
+enum { CB_F32 = 0, CB_F16 = 1, CB_BF16 = 2 };
+/* activation codes: Crispybits/Kernel/csrc/common.cuh:10 */
+enum { CB_ACT_NONE = 0, CB_ACT_RELU = 1, CB_ACT_SILU = 2 };
+/* decode kernel modes: Crispybits/Kernel/csrc/common.cuh:13 */
+enum { CB_MODE_GEMV = 0, CB_MODE_QKV = 1, CB_MODE_GATEUP = 2 };
+
+/* One packed projection (the Proj record of Crispybits/Kernel/csrc/packed_gemv.cu:15-17,
+ * without the output pointer). */
+typedef struct cb_weight {
+    const int32_t* packed; /* [n, ceil(K/32)*bits] */
+    const void* scales;    /* [n, ceil(K/group_size)] */
+    const void* zeros;     /* same shape as scales   */
+    const void* bias;      /* [n] or NULL            */
+    int64_t n;             /* output rows            */
+} cb_weight;
+
+/* Message of the last error raised on this thread ("" if none). */
+const char* cb_last_error(void);
+
+/* Library version string. */
+const char* cb_version(void);
+
+/* Decode GEMV  out[B,n] = act(x[B,K] * W^T + bias).
+ * Replaces packed_gemv_cuda (Crispybits/Kernel/csrc/packed_gemv.cu:252-269; bindings.cpp:33).
+ * split_k >= 1 is clamped to ceil(K/32); rho is the number of resident CTAs per SM the grid is
+ * sized for (0 = one CTA per work unit), as in host_utils.h:90-93.  scratch may be NULL when
+ * split_k == 1. */
+int cb_packed_gemv(const void* x, int64_t B, const cb_weight* w, void* out,
+                   int64_t K, int bits, int64_t group_size, int dtype,
+                   int64_t split_k, int64_t rho, int act,
+                   void* scratch, size_t scratch_bytes, void* stream);
+
+/* Fused gate/up decode  out[B,n] = silu(x Wg^T) * (x Wu^T); gate and up have equal shapes and no bias.
+ * Replaces fused_gate_up_cuda (packed_gemv.cu:317-337; bindings.cpp:35). */
+int cb_fused_gate_up(const void* x, int64_t B, const cb_weight* gate, const cb_weight* up, void* out,
+                     int64_t K, int bits, int64_t group_size, int dtype,
+                     int64_t split_k, int64_t rho,
+                     void* scratch, size_t scratch_bytes, void* stream);
+
+/* Fused Q/K/V decode with optional biases and optional in-kernel RoPE.
+ * Replaces fused_qkv_cuda (packed_gemv.cu:271-315; bindings.cpp:36).
+ * perm_hd > 0 says Q and K rows are stored pair-interleaved per head of that size; outputs are
+ * written in the original column order.  rope_cos / rope_sin are float32 [B, head_dim] or NULL;
+ * RoPE needs perm_hd == head_dim. */
+int cb_fused_qkv(const void* x, int64_t B,
+                 const cb_weight* q, const cb_weight* k, const cb_weight* v,
+                 void* out_q, void* out_k, void* out_v,
+                 const float* rope_cos, const float* rope_sin, int64_t head_dim, int64_t perm_hd,
+                 int64_t K, int bits, int64_t group_size, int dtype,
+                 int64_t split_k, int64_t rho,
+                 void* scratch, size_t scratch_bytes, void* stream);
+
+/* Prefill GEMM  out[M,n] = act(x[M,K] * Wdq^T + bias), float32 accumulation.
+ * Replaces packed_gemm_cuda (Crispybits/Kernel/csrc/packed_gemm.cu:182-203; bindings.cpp:34).
+ * With use_tensor_cores != 0 and a 16-bit dtype the dequantised weight is rounded to dtype before
+ * the product (packed_gemm.cu:56,60) and the tcgen05 kernel is used when the shape allows it. */
+int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out,
+                   int64_t K, int bits, int64_t group_size, int dtype,
+                   int act, int use_tensor_cores, void* stream);
+
+/* Bit-exact unpack  codes[n,K] (int32) <- packed[n, ceil(K/32)*bits]; the device counterpart of
+ * unpack_codes (Crispybits/Kernel/crispybits_kernels/reference.py:58-67; csrc/bitpack.cuh:10-18),
+ * exported so that the integer layout can be checked bit-for-bit against the oracle. */
+int cb_unpack_codes(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, void* stream);
+
+/* Bytes of decode scratch needed for a call with batch B, V virtual output rows (n for GEMV,
+ * nq+nk+nv for QKV, 2n for gate/up) and this split_k.  Takes the place of the per-call
+ * torch::empty of packed_gemv.cu:194-196 and the job-queue workspace of host_utils.h:38-47. */
+size_t cb_gemv_scratch_bytes(int64_t B, int64_t V, int64_t split_k);
+
+/* Introspection used by the Split-K policy (packed_gemv.cu:339-347; bindings.cpp:37-39). */
+int cb_sm_count(void);                 /* SMs of the current device, or -1 on error     */
+int cb_tile_n(void);                   /* virtual output rows per decode work tile       */
+int cb_max_rho(int bits, int mode);    /* occupancy-limited resident CTAs per SM, -1 on error */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CRISPYBITS_B200_H */

@@ -1,0 +1,247 @@
+// extern "C" entry points of libcrispybits_b200.so: argument checks, scratch layout, kernel choice.
+// The host launchers of the reference that this file stands in for are
+// Crispybits/Kernel/csrc/packed_gemv.cu:182-337 and packed_gemm.cu:158-203 (libtorch-typed); the checks
+// mirror Crispybits/Kernel/csrc/host_utils.h:49-87 as far as raw pointers allow (shape and dtype
+// agreement of tensors is checked by the Python shim, which still sees tensors).
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "cb_common.cuh"
+#include "cb_gemv_generic.cuh"
+
+namespace cb {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int sm_count_current() {
+    static int cached[64];  // zero-initialised; device ordinals above 63 are queried each time
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { set_error("cudaGetDevice failed"); return -1; }
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+        set_error("cannot query the SM count of device %d", dev);
+        return -1;
+    }
+    if (dev >= 0 && dev < 64) cached[dev] = sms;
+    return sms;
+}
+
+int launch_unpack(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, cudaStream_t stream);
+int launch_gemm_simt(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
+                     int64_t gs, int act, int round_w, cudaStream_t stream);
+
+namespace {
+
+constexpr size_t kCounterAlign = 256;
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+size_t counter_bytes(int64_t B, int64_t V) {
+    const int64_t n = ceil_div(B, kMaxBatchBlock) * ceil_div(V, kTileN);
+    return (size_t)ceil_div(n * (int64_t)sizeof(int), (int64_t)kCounterAlign) * kCounterAlign;
+}
+
+#define CB_REQUIRE(cond, ...)                 \
+    do {                                      \
+        if (!(cond)) {                        \
+            cb::set_error(__VA_ARGS__);       \
+            return CB_ERR_INVALID;            \
+        }                                     \
+    } while (0)
+
+int check_common(const char* who, const void* x, int64_t B, int64_t K, int bits, int64_t gs, int dtype) {
+    CB_REQUIRE(B >= 0, "%s: negative batch", who);
+    CB_REQUIRE(K > 0 && K < (1ll << 30), "%s: in_features out of range", who);
+    CB_REQUIRE(bits == 2 || bits == 3 || bits == 4, "%s: bits must be 2/3/4", who);
+    CB_REQUIRE(gs > 0 && gs % 32 == 0, "%s: group_size must be a positive multiple of 32", who);
+    CB_REQUIRE(dtype == CB_F32 || dtype == CB_F16 || dtype == CB_BF16, "%s: dtype must be fp32/fp16/bf16", who);
+    CB_REQUIRE(B == 0 || x != nullptr, "%s: x is NULL", who);
+    return CB_OK;
+}
+
+int check_weight(const char* who, const cb_weight* w, int bits) {
+    CB_REQUIRE(w != nullptr, "%s: weight record is NULL", who);
+    CB_REQUIRE(w->n > 0 && w->n < (1ll << 30), "%s: out_features out of range", who);
+    CB_REQUIRE(w->packed && w->scales && w->zeros, "%s: packed/scales/zeros must not be NULL", who);
+    // vector loads of whole chunks: 16 B for W4, 8 B for W2, 4 B for W3 (host_utils.h:66-68)
+    const uintptr_t align = bits == 4 ? 16 : (bits == 2 ? 8 : 4);
+    CB_REQUIRE(reinterpret_cast<uintptr_t>(w->packed) % align == 0,
+               "%s: packed storage must be %d-byte aligned for W%d", who, (int)align, bits);
+    const size_t esz = 2;  // scales/zeros/bias elements are at least 2 bytes
+    CB_REQUIRE(reinterpret_cast<uintptr_t>(w->scales) % esz == 0 && reinterpret_cast<uintptr_t>(w->zeros) % esz == 0,
+               "%s: misaligned scales/zeros", who);
+    return CB_OK;
+}
+
+Proj make_proj(const cb_weight* w, void* out) {
+    Proj p{};
+    p.w = reinterpret_cast<const uint32_t*>(w->packed);
+    p.s = w->scales; p.z = w->zeros; p.b = w->bias; p.out = out; p.n = (int)w->n;
+    return p;
+}
+
+// Fill the derived fields, carve the scratch, pick the kernel and launch.
+int run_decode(const char* who, const void* x, GemvParams& P, int bits, int64_t gs, int dtype, int64_t split_k,
+               int64_t rho, void* scratch, size_t scratch_bytes, cudaStream_t stream) {
+    CB_REQUIRE(split_k >= 1, "%s: split_k must be >= 1", who);
+    CB_REQUIRE((int64_t)P.V * (int64_t)std::max(P.B, 1) < (1ll << 31), "%s: problem too large", who);
+    P.nchunks = (int)ceil_div(P.K, 32);
+    P.wpr = P.nchunks * bits;
+    P.groups = (int)ceil_div(P.K, gs);
+    P.group_size = (int)gs;
+    P.split_k = (int)std::max<int64_t>(1, std::min<int64_t>(split_k, P.nchunks));
+    P.ntiles = (int)ceil_div(P.V, kTileN);
+    P.nbblocks = (int)ceil_div(P.B, kMaxBatchBlock);
+    const int64_t units = (int64_t)P.ntiles * P.nbblocks * P.split_k;
+    CB_REQUIRE(units < (1ll << 31), "%s: too many work units", who);
+    P.units = (int)units;
+    P.partial = nullptr;
+    P.counters = nullptr;
+    if (P.split_k > 1) {
+        const size_t need = cb_gemv_scratch_bytes(P.B, P.V, P.split_k);
+        CB_REQUIRE(scratch != nullptr && scratch_bytes >= need,
+                   "%s: split_k=%d needs %zu bytes of zero-initialised scratch, got %zu", who, P.split_k, need,
+                   scratch_bytes);
+        CB_REQUIRE(reinterpret_cast<uintptr_t>(scratch) % 16 == 0, "%s: scratch must be 16-byte aligned", who);
+        P.counters = reinterpret_cast<int*>(scratch);
+        P.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + counter_bytes(P.B, P.V));
+    }
+    switch (bits) {
+        case 2: return launch_gemv_generic_w2(dtype, x, P, rho, stream);
+        case 3: return launch_gemv_generic_w3(dtype, x, P, rho, stream);
+        default: return launch_gemv_generic_w4(dtype, x, P, rho, stream);
+    }
+}
+
+}  // namespace
+}  // namespace cb
+
+using namespace cb;
+
+extern "C" {
+
+const char* cb_last_error(void) { return g_err; }
+const char* cb_version(void) { return "crispybits_b200 0.1 (sm_100a)"; }
+
+size_t cb_gemv_scratch_bytes(int64_t B, int64_t V, int64_t split_k) {
+    if (B <= 0 || V <= 0 || split_k <= 1) return 0;
+    return counter_bytes(B, V) + (size_t)split_k * (size_t)B * (size_t)V * sizeof(float);
+}
+
+int cb_sm_count(void) { return sm_count_current(); }
+int cb_tile_n(void) { return kTileN; }
+
+int cb_max_rho(int bits, int mode) {
+    if (!(bits == 2 || bits == 3 || bits == 4)) { set_error("cb_max_rho: bits must be 2/3/4"); return -1; }
+    if (mode < CB_MODE_GEMV || mode > CB_MODE_GATEUP) { set_error("cb_max_rho: unknown mode %d", mode); return -1; }
+    const int r = bits == 2 ? occupancy_gemv_generic_w2() : bits == 3 ? occupancy_gemv_generic_w3()
+                                                                    : occupancy_gemv_generic_w4();
+    if (r < 0) set_error("cb_max_rho: occupancy query failed");
+    return r;
+}
+
+int cb_packed_gemv(const void* x, int64_t B, const cb_weight* w, void* out, int64_t K, int bits,
+                   int64_t group_size, int dtype, int64_t split_k, int64_t rho, int act, void* scratch,
+                   size_t scratch_bytes, void* stream) {
+    int rc = check_common("packed_gemv", x, B, K, bits, group_size, dtype);
+    if (rc) return rc;
+    if ((rc = check_weight("packed_gemv", w, bits))) return rc;
+    CB_REQUIRE(act >= 0 && act <= 2, "packed_gemv: act must be 0 (none), 1 (relu) or 2 (silu)");
+    CB_REQUIRE(split_k >= 1, "packed_gemv: split_k must be >= 1");
+    if (B == 0) return CB_OK;
+    CB_REQUIRE(out != nullptr, "packed_gemv: out is NULL");
+    GemvParams P{};
+    P.mode = CB_MODE_GEMV;
+    P.p[0] = make_proj(w, out);
+    P.p[1] = P.p[0]; P.p[2] = P.p[0];
+    P.V = (int)w->n; P.B = (int)B; P.K = (int)K; P.act = act;
+    return run_decode("packed_gemv", x, P, bits, group_size, dtype, split_k, rho, scratch, scratch_bytes,
+                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cb_fused_gate_up(const void* x, int64_t B, const cb_weight* gate, const cb_weight* up, void* out, int64_t K,
+                     int bits, int64_t group_size, int dtype, int64_t split_k, int64_t rho, void* scratch,
+                     size_t scratch_bytes, void* stream) {
+    int rc = check_common("fused_gate_up", x, B, K, bits, group_size, dtype);
+    if (rc) return rc;
+    if ((rc = check_weight("fused_gate_up(gate)", gate, bits))) return rc;
+    if ((rc = check_weight("fused_gate_up(up)", up, bits))) return rc;
+    CB_REQUIRE(gate->n == up->n, "fused_gate_up: gate/up shapes must match");
+    CB_REQUIRE(split_k >= 1, "fused_gate_up: split_k must be >= 1");
+    if (B == 0) return CB_OK;
+    CB_REQUIRE(out != nullptr, "fused_gate_up: out is NULL");
+    GemvParams P{};
+    P.mode = CB_MODE_GATEUP;
+    P.p[0] = make_proj(gate, out); P.p[0].b = nullptr;
+    P.p[1] = make_proj(up, out);   P.p[1].b = nullptr;
+    P.p[2] = P.p[0];
+    P.V = 2 * (int)gate->n; P.B = (int)B; P.K = (int)K; P.act = 0;
+    return run_decode("fused_gate_up", x, P, bits, group_size, dtype, split_k, rho, scratch, scratch_bytes,
+                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cb_fused_qkv(const void* x, int64_t B, const cb_weight* q, const cb_weight* k, const cb_weight* v,
+                 void* out_q, void* out_k, void* out_v, const float* rope_cos, const float* rope_sin,
+                 int64_t head_dim, int64_t perm_hd, int64_t K, int bits, int64_t group_size, int dtype,
+                 int64_t split_k, int64_t rho, void* scratch, size_t scratch_bytes, void* stream) {
+    int rc = check_common("fused_qkv", x, B, K, bits, group_size, dtype);
+    if (rc) return rc;
+    if ((rc = check_weight("fused_qkv(q)", q, bits))) return rc;
+    if ((rc = check_weight("fused_qkv(k)", k, bits))) return rc;
+    if ((rc = check_weight("fused_qkv(v)", v, bits))) return rc;
+    CB_REQUIRE(split_k >= 1, "fused_qkv: split_k must be >= 1");
+    CB_REQUIRE(perm_hd >= 0, "fused_qkv: perm head_dim must be >= 0");
+    if (perm_hd > 0) {
+        CB_REQUIRE(perm_hd % 2 == 0, "fused_qkv: perm head_dim must be even");
+        CB_REQUIRE(q->n % perm_hd == 0 && k->n % perm_hd == 0, "fused_qkv: Q/K widths must be multiples of head_dim");
+    }
+    const bool rope = rope_cos != nullptr;
+    if (rope) {
+        CB_REQUIRE(rope_sin != nullptr, "fused_qkv: cos given without sin");
+        CB_REQUIRE(perm_hd > 0 && perm_hd == head_dim,
+                   "fused_qkv: fused RoPE needs Q/K stored pair-interleaved with the same head_dim");
+    }
+    if (B == 0) return CB_OK;
+    CB_REQUIRE(out_q && out_k && out_v, "fused_qkv: an output pointer is NULL");
+    GemvParams P{};
+    P.mode = CB_MODE_QKV;
+    P.p[0] = make_proj(q, out_q); P.p[1] = make_proj(k, out_k); P.p[2] = make_proj(v, out_v);
+    P.V = (int)(q->n + k->n + v->n); P.B = (int)B; P.K = (int)K; P.act = 0;
+    P.perm_hd = (int)perm_hd;
+    if (rope) { P.rope_cos = rope_cos; P.rope_sin = rope_sin; P.head_dim = (int)head_dim; }
+    return run_decode("fused_qkv", x, P, bits, group_size, dtype, split_k, rho, scratch, scratch_bytes,
+                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
+                   int64_t group_size, int dtype, int act, int use_tensor_cores, void* stream) {
+    int rc = check_common("packed_gemm", x, M, K, bits, group_size, dtype);
+    if (rc) return rc;
+    if ((rc = check_weight("packed_gemm", w, bits))) return rc;
+    CB_REQUIRE(act >= 0 && act <= 2, "packed_gemm: act must be 0 (none), 1 (relu) or 2 (silu)");
+    if (M == 0) return CB_OK;
+    CB_REQUIRE(out != nullptr, "packed_gemm: out is NULL");
+    CB_REQUIRE(M < (1ll << 30), "packed_gemm: M out of range");
+    const int round_w = (use_tensor_cores && dtype != CB_F32) ? 1 : 0;
+    return launch_gemm_simt(dtype, x, M, w, out, K, bits, group_size, act, round_w,
+                            reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cb_unpack_codes(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, void* stream) {
+    CB_REQUIRE(bits == 2 || bits == 3 || bits == 4, "unpack_codes: bits must be 2/3/4");
+    CB_REQUIRE(n >= 0 && K >= 0 && K < (1ll << 30), "unpack_codes: bad shape");
+    if (n == 0 || K == 0) return CB_OK;
+    CB_REQUIRE(packed && codes, "unpack_codes: NULL pointer");
+    return launch_unpack(packed, n, K, bits, codes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,129 @@
+// Shared device/host definitions of the packed W2/W3/W4 linear kernels (sm_100a).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <type_traits>
+
+#include "../../include/crispybits_b200.h"
+
+namespace cb {
+
+constexpr int kTileN = 16;        // virtual output rows per decode work tile (what cb_tile_n() reports)
+constexpr int kMaxBatchBlock = 8; // batch rows that share one pass over the weights
+
+// ---- element conversion -------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Activation codes follow the reference (Crispybits/Kernel/csrc/common.cuh:15-19): relu, or
+// silu computed as v / (1 + exp(-v)).
+__device__ __forceinline__ float activate(float v, int act) {
+    if (act == CB_ACT_RELU) return fmaxf(v, 0.f);
+    if (act == CB_ACT_SILU) return v / (1.0f + __expf(-v));
+    return v;
+}
+
+// ---- decode problem description -----------------------------------------------------------
+struct Proj {
+    const uint32_t* w;  // packed words, row-major
+    const void* s;      // scales [n, groups]
+    const void* z;      // zeros  [n, groups]
+    const void* b;      // bias [n] or nullptr
+    void* out;          // [B, n]
+    int n;
+};
+
+struct GemvParams {
+    Proj p[3];
+    int mode;                 // CB_MODE_*
+    int V, B, K;              // virtual rows, batch, in_features
+    int nchunks, wpr, groups, group_size;
+    int split_k, ntiles, nbblocks, units;
+    int act;
+    float* partial;           // [split_k, B, V] fp32, only when split_k > 1
+    int* counters;            // [nbblocks * ntiles] arrival counters, zero between calls
+    const float* rope_cos;    // [B, head_dim] fp32 or nullptr
+    const float* rope_sin;
+    int head_dim, perm_hd;
+};
+
+// Virtual row -> (projection, row inside it).  GEMV: identity; QKV: three consecutive ranges;
+// gate/up: even virtual rows are gate rows, odd ones the up row of the same index, so that the two
+// operands of silu(gate)*up are neighbours (Crispybits/Kernel/csrc/packed_gemv.cu:33-42).
+__device__ __forceinline__ void map_row(const GemvParams& P, int v, int& proj, int& r) {
+    if (P.mode == CB_MODE_GATEUP) { proj = v & 1; r = v >> 1; }
+    else if (P.mode == CB_MODE_QKV) {
+        const int n0 = P.p[0].n, n1 = P.p[1].n;
+        if (v < n0) { proj = 0; r = v; }
+        else if (v < n0 + n1) { proj = 1; r = v - n0; }
+        else { proj = 2; r = v - n0 - n1; }
+    } else { proj = 0; r = v; }
+}
+
+// Stored (pair-interleaved) row of a head -> original row: even stored positions hold the first
+// half of the head, odd ones the second half (Crispybits/Kernel/csrc/common.cuh:66-70).
+__device__ __forceinline__ int unpermute_row(int r, int hd) {
+    if (hd <= 0) return r;
+    const int head = r / hd, p = r - head * hd;
+    return head * hd + ((p & 1) ? (p >> 1) + hd / 2 : (p >> 1));
+}
+
+template <typename T>
+__device__ __forceinline__ float bias_at(const void* b, int r) {
+    return b ? to_f32(reinterpret_cast<const T*>(b)[r]) : 0.f;
+}
+
+// Final step for one (batch row, virtual row): `mine` is the finished dot product of virtual row v,
+// `partner` that of v^1 (needed by gate/up and by RoPE).  Semantics follow
+// Crispybits/Kernel/csrc/packed_gemv.cu:54-81.
+template <typename T>
+__device__ __forceinline__ void epilogue(const GemvParams& P, int b, int v, float mine, float partner) {
+    int proj, r;
+    map_row(P, v, proj, r);
+    if (P.mode == CB_MODE_GEMV) {
+        const float y = activate(mine + bias_at<T>(P.p[0].b, r), P.act);
+        reinterpret_cast<T*>(P.p[0].out)[(size_t)b * P.p[0].n + r] = from_f32<T>(y);
+    } else if (P.mode == CB_MODE_GATEUP) {
+        if (proj != 0) return;  // the gate row writes silu(gate) * up
+        const float y = activate(mine, CB_ACT_SILU) * partner;
+        reinterpret_cast<T*>(P.p[0].out)[(size_t)b * P.p[0].n + r] = from_f32<T>(y);
+    } else {
+        const Proj& pr = P.p[proj];
+        float y = mine + bias_at<T>(pr.b, r);
+        const int hd = proj < 2 ? P.perm_hd : 0;
+        const int orig = unpermute_row(r, hd);
+        if (P.rope_cos != nullptr && proj < 2) {
+            const float yp = partner + bias_at<T>(pr.b, r ^ 1);
+            const int d = orig % P.head_dim;
+            const float c = P.rope_cos[(size_t)b * P.head_dim + d];
+            const float s = P.rope_sin[(size_t)b * P.head_dim + d];
+            y = (d < P.head_dim / 2) ? (y * c - yp * s) : (y * c + yp * s);
+        }
+        reinterpret_cast<T*>(pr.out)[(size_t)b * pr.n + orig] = from_f32<T>(y);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int sm_count_current();
+
+#define CB_CUDA_TRY(expr)                                                                  \
+    do {                                                                                   \
+        cudaError_t _e = (expr);                                                           \
+        if (_e != cudaSuccess) {                                                           \
+            cb::set_error("%s failed: %s", #expr, cudaGetErrorString(_e));                 \
+            return CB_ERR_CUDA;                                                            \
+        }                                                                                  \
+    } while (0)
+
+}  // namespace cb

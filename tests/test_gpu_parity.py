@@ -1,0 +1,388 @@
+"""GPU parity tests: the CUDA path, called through the package API and the C ABI underneath, against
+the CPU oracle on identical seeded inputs.
+
+Integer work (unpacked codes) must be bit-exact.  Floating outputs are compared with the
+fp32-accumulated dequantise-then-matmul of the oracle's weight; fp16 must stay within 2e-3 maximum
+relative error (max|y-ref| / max|ref|), bf16 within 2e-2, fp32 within 1e-4.  Case lists follow the
+reference's Crispybits/Kernel/tests/test_correctness.py.
+"""
+import functools
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import NAME, TOL, close, make, make_dict, ref_linear, rel_err, rope_tables, to_weight
+from oracle import cb_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True, scope="module")
+def _cuda_backend():
+    from crispybits_kernels import ops
+    assert ops._CUDA is not None, f"native library missing: {ops._IMPORT_ERROR}"
+    ops.set_backend("cuda")
+    yield
+
+
+@functools.lru_cache(maxsize=64)
+def cached(n, k, bits, dtype, bias=False, seed=0, gs=128, std=0.05):
+    return make(n, k, bits, dtype, DEV, bias, seed, gs, std)
+
+
+def test_library_reports_b200_geometry():
+    import crispybits_kernels as ck
+    from crispybits_kernels import _C
+    assert "sm_100a" in _C.version()
+    assert ck.sm_count() == torch.cuda.get_device_properties(0).multi_processor_count
+    assert ck.tile_n() == 16
+    for kind in ("gemv", "qkv", "gate_up"):
+        assert ck.max_rho(3, kind) >= 1
+    with pytest.raises(RuntimeError):
+        ck.max_rho(3, "nope")
+
+
+# ------------------------------------------------------------------ integer layout, bit-exact
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("n,k", [(7, 32), (5, 200), (64, 4096), (33, 4128), (3, 11008)])
+def test_unpack_codes_bit_exact(bits, n, k):
+    from crispybits_kernels import _C
+    rng = np.random.default_rng(bits * 1000 + k)
+    q = rng.integers(0, 1 << bits, size=(n, k), dtype=np.int32)
+    packed = O.pack_codes(q, bits)
+    got = _C.unpack_codes(torch.from_numpy(packed).to(DEV), bits, k).cpu().numpy()
+    assert np.array_equal(got, q)
+
+
+def test_unpack_golden_bit_exact(golden):
+    from crispybits_kernels import _C
+    for tag in [c for c in golden["cases"].tolist() if c.startswith("lin_")]:
+        bits, k = int(tag.split("_")[1][1:]), int(tag.split("_")[2].split("x")[1])
+        got = _C.unpack_codes(torch.from_numpy(golden[f"{tag}/packed"]).to(DEV), bits, k).cpu().numpy()
+        assert np.array_equal(got, golden[f"{tag}/unpacked"]), tag
+
+
+# ------------------------------------------------------------------ golden fixtures through the C ABI
+TD = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}
+GOLD_TOL = {"float16": 2e-3, "bfloat16": 1.6e-2, "float32": 1e-4}
+
+
+def _t(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    return t if dtype is None else t.to(dtype)
+
+
+def test_golden_gemv_and_gemm(golden):
+    from crispybits_kernels import _C
+    for tag in [c for c in golden["cases"].tolist() if c.startswith("lin_")]:
+        _, wb, nk, g, dname = tag.split("_")
+        bits, k, gs, dt = int(wb[1:]), int(nk.split("x")[1]), int(g[1:]), TD[dname]
+        p, s, z = _t(golden[f"{tag}/packed"]), _t(golden[f"{tag}/scales"], dt), _t(golden[f"{tag}/zeros"], dt)
+        bias = _t(golden[f"{tag}/bias"], dt) if f"{tag}/bias" in golden else torch.empty(0, device=DEV, dtype=dt)
+        x, xm = _t(golden[f"{tag}/x"], dt), _t(golden[f"{tag}/xm"], dt)
+        ws = torch.zeros(2, dtype=torch.int32, device=DEV)
+        for split_k in (1, 3):
+            for act in (0, 1, 2):
+                y = _C.packed_gemv(x, p, s, z, bias, bits, k, gs, split_k, 1, act, ws)
+                assert rel_err(y, _t(golden[f"{tag}/gemv_s{split_k}_a{act}"])) < GOLD_TOL[dname], (tag, split_k, act)
+        for tc in (True, False):
+            for act in (0, 2):
+                y = _C.packed_gemm(xm, p, s, z, bias, bits, k, gs, act, tc)
+                assert rel_err(y, _t(golden[f"{tag}/gemm_tc{int(tc)}_a{act}"])) < GOLD_TOL[dname], (tag, tc, act)
+        assert ws.tolist() == [0, 0]
+
+
+def test_golden_fused_ops(golden):
+    from crispybits_kernels import _C
+    h = torch.float16
+    empty = torch.empty(0, device=DEV, dtype=h)
+    ws = torch.zeros(2, dtype=torch.int32, device=DEV)
+    for bits in (2, 3, 4):
+        t = f"gu_w{bits}"
+        g = [_t(golden[f"{t}/gate/packed"]), _t(golden[f"{t}/gate/scales"], h), _t(golden[f"{t}/gate/zeros"], h)]
+        u = [_t(golden[f"{t}/up/packed"]), _t(golden[f"{t}/up/scales"], h), _t(golden[f"{t}/up/zeros"], h)]
+        x = _t(golden[f"{t}/x"], h)
+        for split_k in (1, 2):
+            y = _C.fused_gate_up(x, *g, *u, bits, 256, 128, split_k, 1, ws)
+            assert rel_err(y, _t(golden[f"{t}/out_s{split_k}"])) < 2e-3
+
+        t, hd = f"qkv_w{bits}", 64
+        x = _t(golden[f"{t}/x"], h)
+        prj = {n: [_t(golden[f"{t}/{n}/packed"]), _t(golden[f"{t}/{n}/scales"], h), _t(golden[f"{t}/{n}/zeros"], h),
+                   _t(golden[f"{t}/{n}/bias"], h)] for n in "qkv"}
+        outs = _C.fused_qkv(x, *prj["q"], *prj["k"], *prj["v"], empty, empty, 0, 0, bits, 256, 128, 2, 1, ws)
+        for n, o in zip("qkv", outs):
+            assert rel_err(o, _t(golden[f"{t}/plain_{n}"])) < 2e-3, (t, n)
+        for n in "qk":
+            order = torch.from_numpy(golden[f"{t}/order_{n}"]).to(DEV)
+            prj[n] = [a[order].contiguous() for a in prj[n]]
+        outs = _C.fused_qkv(x, *prj["q"], *prj["k"], *prj["v"], _t(golden[f"{t}/cos"]), _t(golden[f"{t}/sin"]),
+                            hd, hd, bits, 256, 128, 1, 1, ws)
+        for n, o in zip("qkv", outs):
+            assert rel_err(o, _t(golden[f"{t}/rope_{n}"])) < 2e-3, (t, n)
+
+
+# ------------------------------------------------------------------ decode GEMV
+SHAPES = [(128, 256), (300, 200), (4096, 4096), (1024, 5120), (5120, 1024), (33, 4128)]
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("n,k", SHAPES)
+@pytest.mark.parametrize("B", [1, 3])
+def test_gemv(bits, n, k, B):
+    from crispybits_kernels import max_rho, packed_linear
+    w, wd, _ = cached(n, k, bits, torch.float16)
+    x = torch.randn(B, k, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(B))
+    ref = ref_linear(x, wd)
+    for split_k in (1, 2, 7, None):
+        for rho in sorted({0, 1, max(1, max_rho(bits))}):
+            close(packed_linear(x, w, split_k, rho), ref, torch.float16)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("B", [2, 4, 8, 11])
+def test_gemv_batches_share_one_weight_pass(bits, B):
+    from crispybits_kernels import packed_linear
+    w, wd, bd = cached(1000, 1536, bits, torch.float16, True)
+    x = torch.randn(B, 1536, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(7))
+    for split_k in (1, 5, None):
+        y = packed_linear(x, w, split_k, 1, decode_threshold=16)
+        close(y, ref_linear(x, wd, bd), torch.float16)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("act", [None, "relu", "silu"])
+@pytest.mark.parametrize("split_k", [1, 4])
+def test_gemv_bias_act_dtypes(dtype, act, split_k):
+    from crispybits_kernels import packed_linear
+    w, wd, bd = cached(1000, 768, 3, dtype, True)
+    x = torch.randn(2, 768, device=DEV, dtype=dtype)
+    close(packed_linear(x, w, split_k, 2, act), ref_linear(x, wd, bd, act), dtype)
+
+
+@pytest.mark.parametrize("gs", [32, 64, 256])
+def test_group_sizes(gs):
+    from crispybits_kernels import packed_linear
+    w, wd, _ = cached(200, 640, 3, torch.float16, False, 0, gs)
+    x = torch.randn(1, 640, device=DEV, dtype=torch.float16)
+    close(packed_linear(x, w, 3, 1), ref_linear(x, wd), torch.float16)
+
+
+def test_workspace_stays_zero_over_mixed_calls():
+    from crispybits_kernels import new_workspace, packed_linear
+    w, wd, _ = cached(5120, 1024, 3, torch.float16)
+    x = torch.randn(1, 1024, device=DEV, dtype=torch.float16)
+    ws = new_workspace(DEV)
+    for pk, rho in [(1, 1), (4, 2), (1, 0), (7, 1), (1, 3)] * 3:
+        y = packed_linear(x, w, pk, rho, workspace=ws)
+        assert torch.isfinite(y).all()
+        close(y, ref_linear(x, wd), torch.float16)
+    torch.cuda.synchronize()
+    assert ws.tolist() == [0, 0]
+
+
+def test_split_k_scratch_counters_are_left_zero():
+    from crispybits_kernels import _C, packed_linear
+    w, wd, _ = cached(1024, 5120, 4, torch.float16)
+    x = torch.randn(3, 5120, device=DEV, dtype=torch.float16)
+    for pk in (2, 9, 160):
+        close(packed_linear(x, w, pk, 1), ref_linear(x, wd), torch.float16)
+    torch.cuda.synchronize()
+    st = torch.cuda.current_stream().cuda_stream
+    buf = _C._scratch[(torch.cuda.current_device(), st)]
+    ncounters = -(-1024 // 16)
+    assert int(buf[: ncounters * 4].view(torch.int32).abs().sum()) == 0
+
+
+def test_results_do_not_depend_on_arrival_order():
+    """The Split-K fix-up adds partial sums in split order: repeated calls are bit-identical."""
+    from crispybits_kernels import packed_linear
+    w, _, _ = cached(4096, 4096, 3, torch.float16)
+    x = torch.randn(2, 4096, device=DEV, dtype=torch.float16)
+    first = packed_linear(x, w, 6, 2)
+    for _ in range(5):
+        assert torch.equal(packed_linear(x, w, 6, 2), first)
+
+
+# ------------------------------------------------------------------ prefill GEMM
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("M", [5, 33, 130])
+@pytest.mark.parametrize("act", [None, "relu"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_prefill_gemm(bits, M, act, dtype):
+    from crispybits_kernels import packed_linear
+    w, wd, bd = cached(260, 400, bits, dtype, True)
+    x = torch.randn(M, 400, device=DEV, dtype=dtype)
+    tol = TOL[torch.bfloat16] if dtype == torch.bfloat16 else 3e-3   # reference bound for the rounded-weight path
+    close(packed_linear(x, w, act=act), ref_linear(x, wd, bd, act), dtype, tol)
+    close(packed_linear(x, w, act=act, use_tensor_cores=False), ref_linear(x, wd, bd, act), dtype,
+          TOL[torch.bfloat16] if dtype == torch.bfloat16 else 2e-3)
+
+
+# ------------------------------------------------------------------ fused gate/up and QKV
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("B", [1, 4])
+@pytest.mark.parametrize("split_k", [1, 3, None])
+def test_fused_gate_up(bits, B, split_k):
+    from crispybits_kernels import fused_gate_up
+    g, gd, _ = cached(1376, 512, bits, torch.float16, False, 1)
+    u, ud, _ = cached(1376, 512, bits, torch.float16, False, 2)
+    x = torch.randn(B, 512, device=DEV, dtype=torch.float16)
+    ref = torch.nn.functional.silu(x.float() @ gd.T) * (x.float() @ ud.T)
+    close(fused_gate_up(x, g, u, split_k, 2), ref, torch.float16)
+
+
+def test_fused_gate_up_prefill_route():
+    from crispybits_kernels import fused_gate_up
+    g, gd, _ = cached(384, 256, 4, torch.float16, False, 1)
+    u, ud, _ = cached(384, 256, 4, torch.float16, False, 2)
+    x = torch.randn(9, 256, device=DEV, dtype=torch.float16)
+    ref = torch.nn.functional.silu(x.float() @ gd.T) * (x.float() @ ud.T)
+    close(fused_gate_up(x, g, u), ref, torch.float16, 3e-3)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("B", [1, 3, 6])
+@pytest.mark.parametrize("split_k", [1, 5])
+@pytest.mark.parametrize("rope,head_dim", [(False, 0), (False, 128), (True, 128), (True, 64)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_fused_qkv_gqa(bits, B, split_k, rope, head_dim, bias):
+    from crispybits_kernels import apply_rope_reference, fused_qkv, permute_for_rope
+    K, nq, nkv, hd = 1024, 8, 2, (head_dim or 128)
+    q, qd, qb = cached(nq * hd, K, bits, torch.float16, bias, 1)
+    k, kd, kb = cached(nkv * hd, K, bits, torch.float16, bias, 2)
+    v, vd, vb = cached(nkv * hd, K, bits, torch.float16, bias, 3)
+    if head_dim:
+        q, k = permute_for_rope(q, head_dim), permute_for_rope(k, head_dim)
+    x = torch.randn(B, K, device=DEV, dtype=torch.float16)
+    rq, rk, rv = ref_linear(x, qd, qb), ref_linear(x, kd, kb), ref_linear(x, vd, vb)
+    r = None
+    if rope:
+        cos, sin = rope_tables(B, head_dim, DEV)
+        rq = apply_rope_reference(rq, cos, sin, head_dim)
+        rk = apply_rope_reference(rk, cos, sin, head_dim)
+        r = (cos, sin, head_dim)
+    oq, ok, ov = fused_qkv(x, q, k, v, split_k, 2, rope=r)
+    tol = 3e-3 if B > 4 else None      # B=6 routes to the prefill GEMM (rounded weights)
+    close(oq, rq, torch.float16, tol); close(ok, rk, torch.float16, tol); close(ov, rv, torch.float16, tol)
+
+
+# ------------------------------------------------------------------ error behaviour
+def test_argument_errors():
+    import crispybits_kernels as ck
+    from crispybits_kernels import _C
+    w, _, _ = cached(256, 256, 3, torch.float16)
+    x = torch.randn(1, 256, device=DEV, dtype=torch.float16)
+    cos, sin = rope_tables(1, 128, DEV)
+    with pytest.raises(ValueError):
+        ck.fused_qkv(x, w, w, w, rope=(cos, sin, 128))
+    with pytest.raises(ValueError):
+        ck.packed_linear(x, ck.permute_for_rope(w, 128))
+    e = torch.empty(0, device=DEV, dtype=torch.float16)
+    ws = torch.zeros(2, dtype=torch.int32, device=DEV)
+    bad = [
+        lambda: _C.packed_gemv(x.cpu(), w.packed, w.scales, w.zeros, e, 3, 256, 128, 1, 1, 0, ws),     # CPU x
+        lambda: _C.packed_gemv(x, w.packed, w.scales, w.zeros, e, 5, 256, 128, 1, 1, 0, ws),           # bits
+        lambda: _C.packed_gemv(x, w.packed, w.scales, w.zeros, e, 3, 256, 48, 1, 1, 0, ws),            # group size
+        lambda: _C.packed_gemv(x, w.packed, w.scales, w.zeros, e, 3, 256, 128, 0, 1, 0, ws),           # split_k
+        lambda: _C.packed_gemv(x, w.packed, w.scales, w.zeros, e, 3, 256, 128, 1, 1, 3, ws),           # act
+        lambda: _C.packed_gemv(x, w.packed, w.scales.float(), w.zeros.float(), e, 3, 256, 128, 1, 1, 0, ws),
+        lambda: _C.packed_gemv(x, w.packed[:, :-1].contiguous(), w.scales, w.zeros, e, 3, 256, 128, 1, 1, 0, ws),
+        lambda: _C.packed_gemv(x, w.packed, w.scales, w.zeros, e[:0].new_zeros(7), 3, 256, 128, 1, 1, 0, ws),
+        lambda: _C.packed_gemm(x[:, :100].contiguous(), w.packed, w.scales, w.zeros, e, 3, 256, 128, 0, True),
+        lambda: _C.fused_qkv(x, w.packed, w.scales, w.zeros, e, w.packed, w.scales, w.zeros, e, w.packed, w.scales,
+                             w.zeros, e, cos, sin, 128, 0, 3, 256, 128, 1, 1, ws),                      # rope w/o perm
+    ]
+    for call in bad:
+        with pytest.raises(RuntimeError):
+            call()
+    assert _C.packed_gemv(x[:0], w.packed, w.scales, w.zeros, e, 3, 256, 128, 1, 1, 0, ws).shape == (0, 256)
+
+
+def test_c_abi_reports_errors_by_code():
+    """Straight ctypes call, no Python-side checks in between."""
+    import ctypes
+    from crispybits_kernels import _C
+    w, _, _ = cached(256, 256, 3, torch.float16)
+    x = torch.randn(1, 256, device=DEV, dtype=torch.float16)
+    out = torch.empty(1, 256, device=DEV, dtype=torch.float16)
+    rec = _C._Weight(w.packed.data_ptr(), w.scales.data_ptr(), w.zeros.data_ptr(), 0, 256)
+    rc = _C._lib.cb_packed_gemv(x.data_ptr(), 1, ctypes.byref(rec), out.data_ptr(), 256, 7, 128, 1, 1, 1, 0, 0, 0, 0)
+    assert rc == 1 and b"bits" in _C._lib.cb_last_error()
+    rc = _C._lib.cb_packed_gemv(x.data_ptr(), 1, ctypes.byref(rec), out.data_ptr(), 256, 3, 128, 1, 4, 1, 0, 0, 0, 0)
+    assert rc == 1 and b"scratch" in _C._lib.cb_last_error()
+    rc = _C._lib.cb_packed_gemv(x.data_ptr(), 1, ctypes.byref(rec), out.data_ptr(), 256, 3, 128, 1, 1, 1, 0, 0, 0,
+                                torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------ streams and graphs
+def test_non_default_stream():
+    from crispybits_kernels import packed_linear
+    w, wd, _ = cached(512, 512, 3, torch.float16)
+    x = torch.randn(1, 512, device=DEV, dtype=torch.float16)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        y = packed_linear(x, w, 3, 1)
+    s.synchronize()
+    close(y, ref_linear(x, wd), torch.float16)
+
+
+@pytest.mark.parametrize("split_k", [1, 4])
+def test_cuda_graph_capture(split_k):
+    from crispybits_kernels import new_workspace, packed_linear
+    w, wd, _ = cached(4096, 4096, 3, torch.float16)
+    x = torch.randn(1, 4096, device=DEV, dtype=torch.float16)
+    ws = new_workspace(DEV)
+    packed_linear(x, w, split_k, 1, workspace=ws)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y = packed_linear(x, w, split_k, 1, workspace=ws)
+    for _ in range(3):
+        x.copy_(torch.randn_like(x)); g.replay(); torch.cuda.synchronize()
+        close(y, ref_linear(x, wd), torch.float16)
+
+
+# ------------------------------------------------------------------ full benchmark sizes: properties
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (11008, 4096), (4096, 11008)])
+def test_full_size_properties(bits, n, k):
+    """At the benchmark's sizes (weights ~ N(0, 0.02)): parity for batch 1..8, exact unpack of the whole
+    matrix, and linearity y(a + b) = y(a) + y(b) up to output rounding."""
+    from crispybits_kernels import _C, packed_linear
+    w, wd, _ = cached(n, k, bits, torch.float16, False, 0, 128, 0.02)
+    codes = _C.unpack_codes(w.packed, bits, k)
+    assert np.array_equal(codes.cpu().numpy(), O.unpack_codes(w.packed.cpu().numpy(), bits, k))
+    gen = torch.Generator(DEV).manual_seed(n + k + bits)
+    for B in (1, 2, 4, 8):
+        x = torch.randn(B, k, device=DEV, dtype=torch.float16, generator=gen)
+        close(packed_linear(x, w, None, 1, decode_threshold=8), ref_linear(x, wd), torch.float16)
+    a = torch.randn(1, k, device=DEV, dtype=torch.float16, generator=gen)
+    b = torch.randn(1, k, device=DEV, dtype=torch.float16, generator=gen)
+    lhs = packed_linear((a.float() + b.float()).half(), w).float()
+    rhs = packed_linear(a, w).float() + packed_linear(b, w).float()
+    assert rel_err(lhs, rhs) < 4e-3
+
+
+@pytest.mark.parametrize("bits", [3, 4])
+def test_config3_fused_equals_concatenated(bits):
+    """Fused QKV / gate-up at Llama-2-7B widths against one GEMV over the row-concatenated matrix."""
+    from crispybits_kernels import PackedLinearWeight, fused_gate_up, fused_qkv, packed_linear
+    K = 4096
+    ws = [cached(4096, K, bits, torch.float16, False, s, 128, 0.02)[0] for s in (1, 2, 3)]
+    x = torch.randn(1, K, device=DEV, dtype=torch.float16)
+    cat = PackedLinearWeight(torch.cat([w.packed for w in ws]), torch.cat([w.scales for w in ws]),
+                             torch.cat([w.zeros for w in ws]), bits, 128, K, 3 * 4096)
+    y = packed_linear(x, cat)
+    for i, o in enumerate(fused_qkv(x, *ws)):
+        assert rel_err(o, y[:, i * 4096:(i + 1) * 4096].float()) < 1e-3
+    g, gd, _ = cached(11008, K, bits, torch.float16, False, 5, 128, 0.02)
+    u, ud, _ = cached(11008, K, bits, torch.float16, False, 6, 128, 0.02)
+    ref = torch.nn.functional.silu(x.float() @ gd.T) * (x.float() @ ud.T)
+    close(fused_gate_up(x, g, u), ref, torch.float16)
