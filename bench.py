@@ -1,0 +1,393 @@
+#!/usr/bin/env python3
+"""Benchmark of the packed W2/W3/W4 linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload gemv|stack]
+
+Prints ONE JSON line.  Workload at N=1 (`gemv`): batch-1 decode GEMVs over 4096x4096 group-128 weights
+at W4, W3 and W2 -- the shapes the headline metric is quoted on.  A step is one pass over COPIES
+distinct weight matrices per bit-width (3*COPIES launches); the matrices of one step add up to more
+than twice the 126 MB L2, so every launch streams its weights from HBM.  `value` is the algorithmic
+bytes of all launches divided by the device time of the timed steps (CUDA events on the launching
+stream around CUDA-graph replays of a step, so Python launch overhead is not in the number).  `e2e`
+times the same GEMVs through the public API with the activations starting in pinned host memory and
+the result read back to the host every call.  `roofline` describes the dominant kernel (the W4 GEMV):
+algorithmic bytes per launch over its average launch duration, against the measured HBM copy
+bandwidth in MEASURED_PEAKS.json.  `cpu_baseline` is the C oracle (OpenMP, all host threads) timed on
+a bounded sample of the same GEMVs on the host cores.
+
+`--impl reference` times only that CPU implementation and prints the same line shape with
+"impl": "reference".
+
+Algorithmic bytes per GEMV: N*ceil(K/32)*bits*4 (packed) + N*ceil(K/128)*2*2 (fp16 scales and zeros)
++ B*K*2 (x) + B*N*2 (y), weights counted once for any batch.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "llm_quantization-kernel_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+N_OUT, K_IN, GROUP = 4096, 4096, 128
+BITS = (4, 3, 2)
+COPIES = 16                 # distinct weight matrices per bit-width and step
+FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+FALLBACK_TFLOPS = 1590.0
+METRIC = "packed W2/3/4 decode GEMV effective HBM bandwidth (4096x4096, group 128, batch 1)"
+# DRAM bytes per W4 4096x4096 launch from the committed ncu capture (profiles/); None until captured
+NCU_TRAFFIC_W4 = None
+
+
+def gemv_bytes(n, k, bits, batch=1, group=GROUP):
+    return n * -(-k // 32) * bits * 4 + n * -(-k // group) * 4 + batch * k * 2 + batch * n * 2
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    return FALLBACK_HBM_GBS, FALLBACK_TFLOPS, "fallback"
+
+
+# ------------------------------------------------------------------ synthetic inputs
+def synth_weight_numpy(bits, seed, n=N_OUT, k=K_IN):
+    """W ~ N(0, 0.02) from a seeded CPU generator, quantised and packed by the oracle (test infrastructure,
+    used here only to PRODUCE inputs and as the CPU baseline)."""
+    from oracle import cb_oracle_c as OC
+    from oracle import cb_oracle as O
+    g = torch.Generator().manual_seed(seed)
+    w = (torch.randn(n, k, generator=g) * 0.02).numpy()
+    q, s, z = OC.quantize_affine(w, bits, GROUP)
+    return dict(packed=OC.pack_codes(q, bits), scales=O.round_to(s, "float16"), zeros=O.round_to(z, "float16"),
+                bits=bits, group_size=GROUP, in_features=k, out_features=n, bias=None)
+
+
+def device_copies(d, device, copies):
+    """`copies` distinct device matrices with the statistics of `d`: the first is d itself, the others are
+    row rotations of it (different addresses and contents, same value distribution)."""
+    from crispybits_kernels import PackedLinearWeight
+    p = torch.from_numpy(d["packed"]).to(device)
+    s = torch.from_numpy(d["scales"]).to(device=device, dtype=torch.float16)
+    z = torch.from_numpy(d["zeros"]).to(device=device, dtype=torch.float16)
+    out = []
+    for c in range(copies):
+        sh = 97 * c
+        out.append(PackedLinearWeight(torch.roll(p, sh, 0).contiguous(), torch.roll(s, sh, 0).contiguous(),
+                                      torch.roll(z, sh, 0).contiguous(), d["bits"], GROUP, d["in_features"],
+                                      d["out_features"]))
+    return out
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in open(self.path):
+            f = [t.strip() for t in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------------ CPU arm
+def cpu_gemv_sample(seconds_per_bits=3.0, min_iters=3, copies=2):
+    """Time the C oracle's decode GEMV (OpenMP over output rows, all host threads) on the benchmark's
+    three 4096x4096 matrices.  Returns (GB/s over the sample, per-bits ms, threads, description)."""
+    from oracle import cb_oracle_c as OC
+    threads = OC.num_threads()
+    g = torch.Generator().manual_seed(123)
+    x = torch.randn(1, K_IN, generator=g).half().float().numpy()
+    total_bytes, total_s, per = 0, 0.0, {}
+    for bits in BITS:
+        ws = [synth_weight_numpy(bits, 10 * bits + c) for c in range(copies)]
+        OC.gemv(x, ws[0]["packed"], ws[0]["scales"], ws[0]["zeros"], bits, K_IN, GROUP, 1)   # warm-up
+        it, t0 = 0, time.perf_counter()
+        while it < min_iters or time.perf_counter() - t0 < seconds_per_bits:
+            d = ws[it % copies]
+            OC.gemv(x, d["packed"], d["scales"], d["zeros"], bits, K_IN, GROUP, 1)
+            it += 1
+        dt = time.perf_counter() - t0
+        per[f"w{bits}_ms"] = dt / it * 1e3
+        total_bytes += it * gemv_bytes(N_OUT, K_IN, bits)
+        total_s += dt
+    sample = (f"C oracle cbo_gemv (OpenMP, {threads} threads), 4096x4096 batch-1 GEMV at W4/W3/W2, "
+              f"{copies} matrices per bit-width, >= {seconds_per_bits:.0f} s per bit-width")
+    return total_bytes / total_s / 1e9, per, threads, sample
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    per_step = max(0.5, min(3.0, 60.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_gemv_sample(per_step / 3, 1)
+    vals, pers = [], []
+    for _ in range(args.steps):
+        v, per, threads, sample = cpu_gemv_sample(per_step / 3, 1)
+        vals.append(v); pers.append(per)
+    value = float(np.mean(vals))
+    wall = time.perf_counter() - t0
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "gemv_4096x4096_w4_w3_w2_b1", "group_size": GROUP,
+                   "note": "CPU implementation of the reference's decode arithmetic on the host cores"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "per_bits_ms": {k: float(np.mean([p[k] for p in pers])) for k in pers[0]},
+        "gpu_launches": 0, "wall_s": wall,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ GPU arm: GEMV workload
+def timed_graph_replays(graphs, steps, warmup, barrier):
+    """Replay each graph once per step; returns per-graph total ms over the timed steps and total ms."""
+    for _ in range(warmup):
+        for g in graphs:
+            g.replay()
+    barrier()
+    torch.cuda.synchronize()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(graphs) + 1)] for _ in range(steps)]
+    for s in range(steps):
+        ev[s][0].record()
+        for i, g in enumerate(graphs):
+            g.replay()
+            ev[s][i + 1].record()
+    torch.cuda.synchronize()
+    barrier()
+    per = [sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(steps)) for i in range(len(graphs))]
+    total = ev[0][0].elapsed_time(ev[steps - 1][len(graphs)])
+    return per, total
+
+
+def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
+    import crispybits_kernels as ck
+    from crispybits_kernels import ops
+    if ops._CUDA is None:
+        raise RuntimeError(f"native library not loaded: {ops._IMPORT_ERROR}")
+    hbm_peak, tf_peak, peak_kind = peaks()
+    weights = {b: device_copies(synth_weight_numpy(b, b), device, COPIES) for b in BITS}
+    g = torch.Generator().manual_seed(1)
+    x_host = torch.randn(1, K_IN, generator=g).half().pin_memory()
+    x = x_host.to(device)
+    ws = ck.new_workspace(device)
+
+    # correctness gate before timing (the reference's benchmark does the same, scripts/bench_gemv.py:22-24)
+    from oracle import cb_oracle as O
+    for b in BITS:
+        d = synth_weight_numpy(b, b)
+        ref = x_host.float().numpy() @ O.dequantized_weight(d).T
+        y = ck.packed_linear(x, weights[b][0], workspace=ws).float().cpu().numpy()
+        err = float(np.abs(y - ref).max() / np.abs(ref).max())
+        assert err < 2e-3, f"W{b} GEMV off by {err:.2e}; not timing"
+
+    # one CUDA graph per bit-width: COPIES back-to-back GEMVs over distinct matrices
+    side = torch.cuda.Stream(device)
+    graphs, outs = [], []
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for b in BITS:
+            for w in weights[b]:
+                ck.packed_linear(x, w, workspace=ws)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    for b in BITS:
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            outs.append([ck.packed_linear(x, w, workspace=ws) for w in weights[b]])
+        graphs.append(gr)
+
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else 0)
+    if rank == 0:
+        sampler.start()
+    per_ms, total_ms = timed_graph_replays(graphs, args.steps, max(3, args.warmup), barrier)
+    clocks = sampler.stop() if rank == 0 else {}
+    total_ms = reduce_max(total_ms)
+    per_ms = [reduce_max(v) for v in per_ms]
+
+    step_bytes = sum(COPIES * gemv_bytes(N_OUT, K_IN, b) for b in BITS)
+    value = world * step_bytes * args.steps / (total_ms * 1e-3) / 1e9
+    gemv = {}
+    for b, ms in zip(BITS, per_ms):
+        us = ms * 1e3 / (args.steps * COPIES)
+        gbs = gemv_bytes(N_OUT, K_IN, b) / (us * 1e-6) / 1e9
+        gemv[f"w{b}"] = {"us": us, "gbs": gbs, "frac_of_hbm_peak": gbs / hbm_peak,
+                         "split_k": ops._resolve(None, 1, 1, N_OUT, K_IN, torch.device(device))}
+    top = gemv["w4"]
+    roofline = {"bound": "hbm", "achieved": top["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                "frac": top["gbs"] / hbm_peak, "traffic": NCU_TRAFFIC_W4, "kernel": "decode GEMV W4 4096x4096 b1",
+                "algorithmic_bytes_per_launch": gemv_bytes(N_OUT, K_IN, 4), "peak_kind": f"of {peak_kind}"}
+
+    # end to end: activations start in pinned host memory, results are read back, every call
+    y_host = torch.empty(1, N_OUT, dtype=torch.float16).pin_memory()
+
+    def e2e_step():
+        for b in BITS:
+            for w in weights[b]:
+                xd = x_host.to(device, non_blocking=True)
+                y = ck.packed_linear(xd, w, workspace=ws)
+                y_host.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = reduce_max(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3))
+    e2e = {"value": world * step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+           "h2d_bytes_per_step": 3 * COPIES * K_IN * 2, "d2h_bytes_per_step": 3 * COPIES * N_OUT * 2,
+           "api": "crispybits_kernels.packed_linear; x from pinned host memory, y copied back per call; "
+                  "packed weights resident on the device as in install_bitmap"}
+
+    extra = {}
+    if rank == 0 and not args.no_gemm:
+        extra["gemm"] = bench_gemm(device, tf_peak, peak_kind)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, per, threads, sample = cpu_gemv_sample()
+        cpu = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample, **per}
+
+    return {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "gemv_4096x4096_w4_w3_w2_b1", "group_size": GROUP, "copies_per_bits": COPIES,
+                   "l2": f"inputs larger than L2: each step streams {step_bytes / 1e6:.0f} MB of distinct weights "
+                         f"(126 MB L2)", "launch": "CUDA graph replay, one graph per bit-width",
+                   "multi_gpu": "independent replicas (single matmuls stay on one GPU)" if world > 1 else "n/a"},
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gemv": gemv, "clocks": clocks,
+        "gpu_launches": args.steps * 3 * COPIES, **extra,
+    }
+
+
+def bench_gemm(device, tf_peak, peak_kind, m=1024, iters=10):
+    """Prefill GEMM at M=1024 over the 4096x4096 W4 and W3 matrices (TFLOP/s = 2*M*N*K / t)."""
+    import crispybits_kernels as ck
+    out = {}
+    x = torch.randn(m, K_IN, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(5))
+    for b in (4, 3):
+        ws = device_copies(synth_weight_numpy(b, b), device, 2)
+        for _ in range(3):
+            ck.packed_linear(x, ws[0])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            ck.packed_linear(x, ws[i % 2])
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / iters
+        tf = 2.0 * m * N_OUT * K_IN / (us * 1e-6) / 1e12
+        out[f"m{m}_4096x4096_w{b}"] = {"us": us, "tflops": tf, "frac_of_dense_peak": tf / tf_peak,
+                                       "peak_kind": f"of {peak_kind}"}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default=None, choices=[None, "gemv", "stack"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM figures")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    device = f"cuda:{local}"
+    torch.backends.cuda.matmul.allow_tf32 = False
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(device))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def reduce_max(v):
+        if dist is None:
+            return float(v)
+        t = torch.tensor([float(v)], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    line = run_gemv_workload(args, rank, world, device, barrier, reduce_max)
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -19,9 +19,10 @@
  *     in `dtype`; `bias` is [n] in `dtype` or NULL.
  *   - Scratch: the decode kernels need device scratch when split_k > 1 (partial sums and
  *     per-tile arrival counters).  The caller owns it: size it with cb_gemv_scratch_bytes(), zero
- *     it ONCE after allocation, and pass it to every call; the kernels leave the counter region
- *     zero again when they finish.  Two calls that may overlap on the GPU (different streams)
- *     need different scratch buffers.
+ *     it ONCE after allocation, and pass it to every call.  The first 256 KiB are the arrival
+ *     counters (the same place for every call, so one buffer serves calls of any shape); the
+ *     kernels leave them zero again when they finish.  Two calls that may overlap on the GPU
+ *     (different streams) need different scratch buffers.
  */
 #ifndef CRISPYBITS_B200_H
 #define CRISPYBITS_B200_H

@@ -41,13 +41,19 @@ int launch_gemm_simt(int dtype, const void* x, int64_t M, const cb_weight* w, vo
 
 namespace {
 
-constexpr size_t kCounterAlign = 256;
+// Scratch layout: a FIXED region of kMaxCounters arrival counters, then the partial sums.  The
+// counter region must not move from call to call: the kernels rely on finding it zero and leave it
+// zero, while the partial-sum region holds stale data between calls.
+constexpr int64_t kMaxCounters = 65536;
+constexpr size_t kCounterBytes = (size_t)kMaxCounters * sizeof(int);
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-size_t counter_bytes(int64_t B, int64_t V) {
-    const int64_t n = ceil_div(B, kMaxBatchBlock) * ceil_div(V, kTileN);
-    return (size_t)ceil_div(n * (int64_t)sizeof(int), (int64_t)kCounterAlign) * kCounterAlign;
+// Split-K is a scheduling hint.  A problem with more (batch block x row tile) pairs than counters
+// already has far more work units than the GPU has SMs, so it runs unsplit.
+inline int64_t effective_split(int64_t B, int64_t V, int64_t split_k) {
+    if (split_k <= 1) return 1;
+    return ceil_div(B, kMaxBatchBlock) * ceil_div(V, kTileN) > kMaxCounters ? 1 : split_k;
 }
 
 #define CB_REQUIRE(cond, ...)                 \
@@ -98,7 +104,7 @@ int run_decode(const char* who, const void* x, GemvParams& P, int bits, int64_t 
     P.wpr = P.nchunks * bits;
     P.groups = (int)ceil_div(P.K, gs);
     P.group_size = (int)gs;
-    P.split_k = (int)std::max<int64_t>(1, std::min<int64_t>(split_k, P.nchunks));
+    P.split_k = (int)std::max<int64_t>(1, std::min<int64_t>(effective_split(P.B, P.V, split_k), P.nchunks));
     P.ntiles = (int)ceil_div(P.V, kTileN);
     P.nbblocks = (int)ceil_div(P.B, kMaxBatchBlock);
     const int64_t units = (int64_t)P.ntiles * P.nbblocks * P.split_k;
@@ -113,7 +119,7 @@ int run_decode(const char* who, const void* x, GemvParams& P, int bits, int64_t 
                    scratch_bytes);
         CB_REQUIRE(reinterpret_cast<uintptr_t>(scratch) % 16 == 0, "%s: scratch must be 16-byte aligned", who);
         P.counters = reinterpret_cast<int*>(scratch);
-        P.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + counter_bytes(P.B, P.V));
+        P.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kCounterBytes);
     }
     switch (bits) {
         case 2: return launch_gemv_generic_w2(dtype, x, P, rho, stream);
@@ -133,8 +139,8 @@ const char* cb_last_error(void) { return g_err; }
 const char* cb_version(void) { return "crispybits_b200 0.1 (sm_100a)"; }
 
 size_t cb_gemv_scratch_bytes(int64_t B, int64_t V, int64_t split_k) {
-    if (B <= 0 || V <= 0 || split_k <= 1) return 0;
-    return counter_bytes(B, V) + (size_t)split_k * (size_t)B * (size_t)V * sizeof(float);
+    if (B <= 0 || V <= 0 || effective_split(B, V, split_k) <= 1) return 0;
+    return kCounterBytes + (size_t)split_k * (size_t)B * (size_t)V * sizeof(float);
 }
 
 int cb_sm_count(void) { return sm_count_current(); }

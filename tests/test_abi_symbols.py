@@ -30,8 +30,8 @@ def test_library_exports_every_declared_symbol():
     lib.cb_gemv_scratch_bytes.restype = ctypes.c_size_t
     lib.cb_gemv_scratch_bytes.argtypes = [ctypes.c_int64] * 3
     assert lib.cb_gemv_scratch_bytes(1, 4096, 1) == 0
-    # counters (256 tiles * 4 B, already a multiple of 256) + 3 partial planes of 4096 floats
-    assert lib.cb_gemv_scratch_bytes(1, 4096, 3) == 1024 + 3 * 4096 * 4
+    # fixed region of 65536 arrival counters + 3 partial planes of 4096 floats
+    assert lib.cb_gemv_scratch_bytes(1, 4096, 3) == 65536 * 4 + 3 * 4096 * 4
 
 
 def test_product_package_does_not_reach_into_the_oracle():
