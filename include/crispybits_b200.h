@@ -100,6 +100,26 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out,
  * exported so that the integer layout can be checked bit-for-bit against the oracle. */
 int cb_unpack_codes(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, void* stream);
 
+/* Decode GEMV with library-owned scratch, for callers that cannot allocate device memory.
+ * No counterpart in the reference (its launcher allocates with torch::empty on every call).
+ * Same arguments and result as cb_packed_gemv, minus the scratch pair: the Split-K partial sums and
+ * arrival counters live in a fixed __device__ array inside the library (cb_static_scratch_bytes()
+ * bytes, held by every GPU that loads the library).  This call makes no cudaMalloc / cudaFree and uses
+ * no allocating routine.  Limits and rules:
+ *   - split_k * B * n must not exceed 262144 (the array's partial-sum room) and
+ *     ceil(B/8) * ceil(n/16) must not exceed 65536; larger requests fail with CB_ERR_INVALID;
+ *   - the first call on each device looks up the array's device address; make that first call
+ *     outside any stream capture;
+ *   - all calls on a device share the one array: calls that can overlap on the GPU (different
+ *     streams, or graphs replayed concurrently) race on it -- serialise them, or give the
+ *     overlapping ones their own buffers through cb_packed_gemv. */
+int cb_packed_gemv_static_scratch(const void* x, int64_t B, const cb_weight* w, void* out,
+                                  int64_t K, int bits, int64_t group_size, int dtype,
+                                  int64_t split_k, int64_t rho, int act, void* stream);
+
+/* Size in bytes of the library-owned scratch array used by cb_packed_gemv_static_scratch. */
+size_t cb_static_scratch_bytes(void);
+
 /* Bytes of decode scratch needed for a call with batch B, V virtual output rows (n for GEMV,
  * nq+nk+nv for QKV, 2n for gate/up) and this split_k.  Takes the place of the per-call
  * torch::empty of packed_gemv.cu:194-196 and the job-queue workspace of host_utils.h:38-47. */
