@@ -125,6 +125,18 @@ size_t cb_static_scratch_bytes(void);
  * torch::empty of packed_gemv.cu:194-196 and the job-queue workspace of host_utils.h:38-47. */
 size_t cb_gemv_scratch_bytes(int64_t B, int64_t V, int64_t split_k);
 
+/* Library options (no counterpart in the reference).  option 0: programmatic dependent launch of the
+ * streamlined decode kernel, value 0/1 (default 1, or 0 when CRISPYBITS_PDL=0 is in the environment).
+ * With it on, a decode call may start fetching PACKED WEIGHTS before the previous kernel of the
+ * stream has finished; activations, outputs and scratch are only touched afterwards.  option 1:
+ * value 1 forces the shape-generic decode kernel everywhere (for A/B checks). */
+void cb_set_option(int option, int value);
+
+/* Synchronises the device, then returns in *status the decode kernels' error word and clears it:
+ * 0 = no problem; k > 0 = a shared-memory copy of pass k-1 did not arrive within the wait limit and
+ * the affected outputs were not written.  No counterpart in the reference. */
+int cb_decode_status(int* status);
+
 /* Introspection used by the Split-K policy (packed_gemv.cu:339-347; bindings.cpp:37-39). */
 int cb_sm_count(void);                 /* SMs of the current device, or -1 on error     */
 int cb_tile_n(void);                   /* virtual output rows per decode work tile       */

@@ -47,8 +47,11 @@ _lib.cb_fused_qkv.argtypes = [_vp, _i64, _WP, _WP, _WP, _vp, _vp, _vp, _vp, _vp,
 _lib.cb_packed_gemm.argtypes = [_vp, _i64, _WP, _vp, _i64, _int, _i64, _int, _int, _int, _vp]
 _lib.cb_unpack_codes.argtypes = [_vp, _i64, _i64, _int, _vp, _vp]
 _lib.cb_max_rho.argtypes = [_int, _int]
+_lib.cb_set_option.argtypes = [_int, _int]
+_lib.cb_set_option.restype = None
+_lib.cb_decode_status.argtypes = [ctypes.POINTER(_int)]
 for _f in ("cb_packed_gemv", "cb_fused_gate_up", "cb_fused_qkv", "cb_packed_gemm", "cb_unpack_codes",
-           "cb_sm_count", "cb_tile_n", "cb_max_rho"):
+           "cb_sm_count", "cb_tile_n", "cb_max_rho", "cb_decode_status"):
     getattr(_lib, _f).restype = _int
 
 _DTYPE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
@@ -161,6 +164,12 @@ def _scratch_for(x: torch.Tensor, stream: int, nbytes: int):
     return buf
 
 
+def _decode_scratch(x, stream: int, B: int, V: int, pk: int):
+    """Scratch for a decode call.  Sized for the requested split and, so that the streamlined kernel may
+    raise the split when its shared-memory budget asks for it, for at least a 4-way split."""
+    return _scratch_for(x, stream, max(_lib.cb_gemv_scratch_bytes(B, V, pk), _lib.cb_gemv_scratch_bytes(B, V, 4)))
+
+
 def _stream(x) -> int:
     return torch.cuda.current_stream(x.device).cuda_stream
 
@@ -182,8 +191,7 @@ def packed_gemv(x, packed, scales, zeros, bias, bits, in_features, group_size, s
     with torch.cuda.device(x.device):
         st = _stream(x)
         pk = max(1, min(split_k, -(-k // 32)))
-        nbytes = _lib.cb_gemv_scratch_bytes(B, n, pk)
-        sc = _scratch_for(x, st, nbytes)
+        sc = _decode_scratch(x, st, B, n, pk)
         w = _weight(packed, scales, zeros, bias)
         _rc(_lib.cb_packed_gemv(x.data_ptr(), B, ctypes.byref(w), out.data_ptr(), k, bits, gs, _DTYPE[x.dtype],
                                 pk, rho, act, _ptr(sc), 0 if sc is None else sc.numel(), st))
@@ -225,7 +233,7 @@ def fused_gate_up(x, wg, sg, zg, wu, su, zu, bits, in_features, group_size, spli
     with torch.cuda.device(x.device):
         st = _stream(x)
         pk = max(1, min(split_k, -(-k // 32)))
-        sc = _scratch_for(x, st, _lib.cb_gemv_scratch_bytes(B, 2 * n, pk))
+        sc = _decode_scratch(x, st, B, 2 * n, pk)
         g, u = _weight(wg, sg, zg, None), _weight(wu, su, zu, None)
         _rc(_lib.cb_fused_gate_up(x.data_ptr(), B, ctypes.byref(g), ctypes.byref(u), out.data_ptr(), k, bits, gs,
                                   _DTYPE[x.dtype], pk, rho, _ptr(sc), 0 if sc is None else sc.numel(), st))
@@ -269,7 +277,7 @@ def fused_qkv(x, wq, sq, zq, bq, wk, sk, zk, bk, wv, sv, zv, bv, rope_cos, rope_
         st = _stream(x)
         pk = max(1, min(split_k, -(-k // 32)))
         V = wq.shape[0] + wk.shape[0] + wv.shape[0]
-        sc = _scratch_for(x, st, _lib.cb_gemv_scratch_bytes(B, V, pk))
+        sc = _decode_scratch(x, st, B, V, pk)
         q, kk, v = _weight(wq, sq, zq, bq), _weight(wk, sk, zk, bk), _weight(wv, sv, zv, bv)
         _rc(_lib.cb_fused_qkv(x.data_ptr(), B, ctypes.byref(q), ctypes.byref(kk), ctypes.byref(v),
                               outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), _ptr(rc), _ptr(rs),
@@ -310,6 +318,18 @@ def max_rho(bits: int, kind: str = "gemv") -> int:
     if r < 0:
         _rc(1)
     return int(r)
+
+
+def set_option(option: int, value: int) -> None:
+    """0: programmatic dependent launch on/off; 1: force the shape-generic decode kernel (A/B checks)."""
+    _lib.cb_set_option(int(option), int(value))
+
+
+def decode_status() -> int:
+    """Synchronise, then read and clear the decode kernels' error word (0 = fine)."""
+    out = _int(0)
+    _rc(_lib.cb_decode_status(ctypes.byref(out)))
+    return int(out.value)
 
 
 def version() -> str:

@@ -5,6 +5,7 @@
 // agreement of tensors is checked by the Python shim, which still sees tensors).
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "cb_common.cuh"
@@ -34,6 +35,21 @@ int sm_count_current() {
     if (dev >= 0 && dev < 64) cached[dev] = sms;
     return sms;
 }
+
+int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, int64_t rho, bool pdl,
+                       void* scratch, size_t scratch_bytes, cudaStream_t stream);
+int stream_status_read_and_clear(int* out);
+
+// Programmatic dependent launch for the streamlined decode kernel (on unless CRISPYBITS_PDL=0).
+static int g_pdl = -1;
+static bool pdl_enabled() {
+    if (g_pdl < 0) {
+        const char* e = getenv("CRISPYBITS_PDL");
+        g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return g_pdl != 0;
+}
+static int g_force_generic = 0;
 
 int launch_unpack(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, cudaStream_t stream);
 int launch_gemm_simt(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
@@ -121,6 +137,11 @@ int run_decode(const char* who, const void* x, GemvParams& P, int bits, int64_t 
         P.counters = reinterpret_cast<int*>(scratch);
         P.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kCounterBytes);
     }
+    if (!g_force_generic) {
+        // the streamlined fp16 kernel when the problem is inside its domain (-1 = it is not)
+        const int rc = launch_gemv_stream(bits, dtype, x, P, rho, pdl_enabled(), scratch, scratch_bytes, stream);
+        if (rc != -1) return rc;
+    }
     switch (bits) {
         case 2: return launch_gemv_generic_w2(dtype, x, P, rho, stream);
         case 3: return launch_gemv_generic_w3(dtype, x, P, rho, stream);
@@ -144,6 +165,16 @@ size_t cb_gemv_scratch_bytes(int64_t B, int64_t V, int64_t split_k) {
 }
 
 int cb_sm_count(void) { return sm_count_current(); }
+
+void cb_set_option(int option, int value) {
+    if (option == 0) g_pdl = value ? 1 : 0;
+    if (option == 1) g_force_generic = value ? 1 : 0;
+}
+
+int cb_decode_status(int* status) {
+    if (status == nullptr) { set_error("cb_decode_status: NULL"); return CB_ERR_INVALID; }
+    return stream_status_read_and_clear(status);
+}
 int cb_tile_n(void) { return kTileN; }
 
 int cb_max_rho(int bits, int mode) {

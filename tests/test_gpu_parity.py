@@ -206,6 +206,45 @@ def test_results_do_not_depend_on_arrival_order():
         assert torch.equal(packed_linear(x, w, 6, 2), first)
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("mode", ["gemv", "gate_up", "qkv_rope"])
+def test_streamlined_kernel_agrees_with_generic_kernel(bits, mode):
+    """Same call through both decode kernels (option 1 forces the generic one)."""
+    from crispybits_kernels import _C, fused_gate_up, fused_qkv, packed_linear, permute_for_rope
+    K = 2048
+    x = torch.randn(3, K, device=DEV, dtype=torch.float16)
+
+    def run():
+        if mode == "gemv":
+            w, _, _ = cached(1000, K, bits, torch.float16, True, 4)
+            return [packed_linear(x, w, sk, 1, "silu") for sk in (1, 3)]
+        if mode == "gate_up":
+            g_, _, _ = cached(1376, K, bits, torch.float16, False, 1)
+            u_, _, _ = cached(1376, K, bits, torch.float16, False, 2)
+            return [fused_gate_up(x, g_, u_, sk, 1) for sk in (1, 2)]
+        q, _, _ = cached(1024, K, bits, torch.float16, True, 1)
+        k, _, _ = cached(256, K, bits, torch.float16, True, 2)
+        v, _, _ = cached(256, K, bits, torch.float16, False, 3)
+        q, k = permute_for_rope(q, 128), permute_for_rope(k, 128)
+        cos, sin = rope_tables(3, 128, DEV)
+        return [o for sk in (1, 4) for o in fused_qkv(x, q, k, v, sk, 1, rope=(cos, sin, 128))]
+
+    fast = run()
+    _C.set_option(1, 1)
+    try:
+        slow = run()
+    finally:
+        _C.set_option(1, 0)
+    for a, b in zip(fast, slow):
+        assert rel_err(a, b.float()) < 1e-3
+    assert _C.decode_status() == 0
+
+
+def test_decode_status_word_is_clean_after_the_suite_so_far():
+    from crispybits_kernels import _C
+    assert _C.decode_status() == 0
+
+
 # ------------------------------------------------------------------ prefill GEMM
 @pytest.mark.parametrize("bits", [2, 3, 4])
 @pytest.mark.parametrize("M", [5, 33, 130])
