@@ -233,7 +233,10 @@ def _resolve(split_k: Optional[int], rho: int, batch: int, v_rows: int, k: int, 
         index = device.index if device.index is not None else torch.cuda.current_device()
     else:
         index = 0
-    split = balanced_split_k(batch, v_rows, tile_n(), _sm_count_for(index), rho, nchunks)
+    # The decode kernels read the weights once per block of up to 8 batch rows and give every CTA an
+    # equal slab of rows, so the underfill rule applies with batch counted in blocks: split K only
+    # when there are fewer 16-row tiles than resident CTAs.
+    split = candidate_split_k(ceil(batch / BATCH_BLOCK), v_rows, tile_n(), _sm_count_for(index), rho)
     return max(1, min(split, nchunks))
 
 

@@ -37,16 +37,33 @@ constexpr int kMaxBuf = 3;
 constexpr int kSpinLimit = 1 << 22;       // bounded mbarrier wait (~ a second), then give up and flag
 constexpr size_t kSmemCap = 220 * 1024;
 
-__device__ int g_stream_status;           // 0 = ok; else the pass whose copy never landed, plus one
+__device__ int g_stream_status;
+#ifdef CB_STREAM_TIMING
+// Diagnostic build only: per-CTA nanosecond timestamps of the kernel's phases.
+__device__ unsigned long long g_stream_times[1024][8];
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define CB_STAMP(i) do { if (threadIdx.x == 0 && blockIdx.x < 1024) { g_stream_times[blockIdx.x][i] = now_ns(); \
+    if ((i) == 0) g_stream_times[blockIdx.x][7] = (unsigned long long)clock64(); \
+    if ((i) == 6) g_stream_times[blockIdx.x][7] = (unsigned long long)clock64() - g_stream_times[blockIdx.x][7]; } } while (0)
+#else
+#define CB_STAMP(i) do { } while (0)
+#endif           // 0 = ok; else the pass whose copy never landed, plus one
 
 struct StreamParams {
     GemvParams g;
     int nslabs;            // CTAs per K-partition
     int nbuf;              // ring depth
     int pitch;             // shared-memory bytes per staged row (row bytes + bank-spreading pad)
-    int xb_stride;         // bytes between batch rows of the x fragments
-    int bpad;              // batch rows staged (>= B)
-    unsigned off_x, off_xsum, off_red, off_ring, off_bar;   // shared-memory carve-up
+    int meta_stride;       // shared-memory bytes per staged row of scales (and of zeros)
+    int slot_bytes;        // one ring slot: 32 weight rows, 32 scale rows, 32 zero rows
+    int xb_stride;         // shared-memory bytes between batch rows of the staged activations
+    int pair_q, pair_r;    // row pairs per slab: quotient and remainder of (V/2) / nslabs
+    int grp_q, grp_r;      // group PAIRS per K-partition: quotient and remainder of (groups/2) / split_k
+    unsigned off_x, off_red, off_ring, off_bar;   // shared-memory carve-up
 };
 
 // ---- small PTX wrappers ------------------------------------------------------------------------
@@ -67,6 +84,17 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+// The mbarrier receives one arrival once all cp.async issued so far by this thread have landed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
     uint32_t r;
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));
@@ -84,98 +112,131 @@ __device__ __forceinline__ uint32_t h2add(uint32_t a, uint32_t b) {
 }
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t a0, const uint32_t a1, const uint32_t a2,
                                          const uint32_t a3, const uint32_t b0, const uint32_t b1, const float (&c)[4]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                  : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 
 constexpr uint32_t kMagic = 0x64006400u;      // half2(1024, 1024)
-constexpr uint32_t kNeg1024 = 0xE400E400u;
 
-// The 32 codes of one chunk -> 16 half2 registers of exact integer values.  e[m] holds the code pair
-// pair_lo<BITS>(m), pair_lo<BITS>(m) + pair_gap<BITS>() (low half, high half).
+__device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+// The 32 codes of one chunk -> 16 half2 registers holding the exact integers (code - zero).  e[m] holds
+// the code pair (pair_lo(m), pair_lo(m) + pair_gap()) in its (low, high) half.  A field that sits at
+// bit p of a half is extracted in place: (w & mask) | 0x6400 reads as 1024 + code * 2^p, and one
+// fused multiply-add with 2^-p and the constant -(1024 * 2^-p + zero) leaves code - zero, exactly.
+// `consts()` prepares those constants for one (row, group) from the group's zero point.
 template <int BITS> struct Unpack;
 
 template <> struct Unpack<4> {
-    // word i: e[4i+j] = (code 8i+j, code 8i+j+4)
-    __device__ static __forceinline__ int pair_lo(int m) { return 8 * (m >> 2) + (m & 3); }
+    static constexpr int kConsts = 2;
+    __device__ static __forceinline__ int pair_lo(int m) { return 8 * (m >> 2) + (m & 3); }   // word i: e[4i+j] = (8i+j, 8i+j+4)
     __device__ static __forceinline__ int pair_gap() { return 4; }
-    __device__ static __forceinline__ void run(const uint32_t (&w)[4], uint32_t (&e)[16]) {
+    __device__ static __forceinline__ void consts(uint32_t zz, uint32_t (&k)[kConsts]) {
+        k[0] = h2sub(0xE400E400u, zz);     // -(1024 + z)
+        k[1] = h2sub(0xD400D400u, zz);     // -(64 + z)
+    }
+    __device__ static __forceinline__ void run(const uint32_t (&w)[4], const uint32_t (&k)[kConsts], uint32_t (&e)[16]) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t lo = w[i], hi = w[i] >> 8;
-            e[4 * i + 0] = h2add(lop3_and_or(lo, 0x000F000Fu, kMagic), kNeg1024);
-            e[4 * i + 1] = h2fma(lop3_and_or(lo, 0x00F000F0u, kMagic), 0x2C002C00u, 0xD400D400u);   // /16, -64
-            e[4 * i + 2] = h2add(lop3_and_or(hi, 0x000F000Fu, kMagic), kNeg1024);
-            e[4 * i + 3] = h2fma(lop3_and_or(hi, 0x00F000F0u, kMagic), 0x2C002C00u, 0xD400D400u);
+            e[4 * i + 0] = h2add(lop3_and_or(lo, 0x000F000Fu, kMagic), k[0]);
+            e[4 * i + 1] = h2fma(lop3_and_or(lo, 0x00F000F0u, kMagic), 0x2C002C00u, k[1]);   // * 1/16
+            e[4 * i + 2] = h2add(lop3_and_or(hi, 0x000F000Fu, kMagic), k[0]);
+            e[4 * i + 3] = h2fma(lop3_and_or(hi, 0x00F000F0u, kMagic), 0x2C002C00u, k[1]);
         }
     }
 };
 
 template <> struct Unpack<2> {
-    // word i: e[8i+j] = (code 16i+j, code 16i+j+8)
-    __device__ static __forceinline__ int pair_lo(int m) { return 16 * (m >> 3) + (m & 7); }
+    static constexpr int kConsts = 5;
+    __device__ static __forceinline__ int pair_lo(int m) { return 16 * (m >> 3) + (m & 7); }  // word i: e[8i+j] = (16i+j, 16i+j+8)
     __device__ static __forceinline__ int pair_gap() { return 8; }
-    __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t (&e)[16]) {
+    __device__ static __forceinline__ void consts(uint32_t zz, uint32_t (&k)[kConsts]) {
+        k[0] = h2sub(0xE400E400u, zz);     // -(1024 + z)
+        k[1] = h2sub(0xDC00DC00u, zz);     // -(256 + z)
+        k[2] = h2sub(0xD400D400u, zz);     // -(64 + z)
+        k[3] = h2sub(0xCC00CC00u, zz);     // -(16 + z)
+        k[4] = h2sub(0xC400C400u, zz);     // -(4 + z)
+    }
+    __device__ static __forceinline__ void run(const uint32_t (&w)[2], const uint32_t (&k)[kConsts], uint32_t (&e)[16]) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const uint32_t lo = w[i], hi = w[i] >> 10;
-            e[8 * i + 0] = h2add(lop3_and_or(lo, 0x00030003u, kMagic), kNeg1024);
-            e[8 * i + 1] = h2fma(lop3_and_or(lo, 0x000C000Cu, kMagic), 0x34003400u, 0xDC00DC00u);   // /4,   -256
-            e[8 * i + 2] = h2fma(lop3_and_or(lo, 0x00300030u, kMagic), 0x2C002C00u, 0xD400D400u);   // /16,  -64
-            e[8 * i + 3] = h2fma(lop3_and_or(lo, 0x00C000C0u, kMagic), 0x24002400u, 0xCC00CC00u);   // /64,  -16
-            e[8 * i + 4] = h2fma(lop3_and_or(lo, 0x03000300u, kMagic), 0x1C001C00u, 0xC400C400u);   // /256, -4
-            e[8 * i + 5] = h2add(lop3_and_or(hi, 0x00030003u, kMagic), kNeg1024);
-            e[8 * i + 6] = h2fma(lop3_and_or(hi, 0x000C000Cu, kMagic), 0x34003400u, 0xDC00DC00u);
-            e[8 * i + 7] = h2fma(lop3_and_or(hi, 0x00300030u, kMagic), 0x2C002C00u, 0xD400D400u);
+            e[8 * i + 0] = h2add(lop3_and_or(lo, 0x00030003u, kMagic), k[0]);
+            e[8 * i + 1] = h2fma(lop3_and_or(lo, 0x000C000Cu, kMagic), 0x34003400u, k[1]);   // * 1/4
+            e[8 * i + 2] = h2fma(lop3_and_or(lo, 0x00300030u, kMagic), 0x2C002C00u, k[2]);   // * 1/16
+            e[8 * i + 3] = h2fma(lop3_and_or(lo, 0x00C000C0u, kMagic), 0x24002400u, k[3]);   // * 1/64
+            e[8 * i + 4] = h2fma(lop3_and_or(lo, 0x03000300u, kMagic), 0x1C001C00u, k[4]);   // * 1/256
+            e[8 * i + 5] = h2add(lop3_and_or(hi, 0x00030003u, kMagic), k[0]);
+            e[8 * i + 6] = h2fma(lop3_and_or(hi, 0x000C000Cu, kMagic), 0x34003400u, k[1]);
+            e[8 * i + 7] = h2fma(lop3_and_or(hi, 0x00300030u, kMagic), 0x2C002C00u, k[2]);
         }
     }
 };
 
 template <> struct Unpack<3> {
     // e[j] = (code j, code j+16): the chunk is a 96-bit stream; code j sits at bit 3j, code j+16 at bit
-    // 3j+48.  Windows of 15 bits (5 codes) of both halves are brought side by side into one register.
+    // 3j+48.  Windows of 15 bits (5 codes) of both halves are brought side by side into one register
+    // with funnel shifts (which also reassemble the codes that straddle a word) and a byte permute.
+    static constexpr int kConsts = 3;
     __device__ static __forceinline__ int pair_lo(int m) { return m; }
     __device__ static __forceinline__ int pair_gap() { return 16; }
-    __device__ static __forceinline__ void five(uint32_t p, uint32_t* e) {
-        const uint32_t q = p >> 9;
-        e[0] = h2add(lop3_and_or(p, 0x00070007u, kMagic), kNeg1024);
-        e[1] = h2fma(lop3_and_or(p, 0x00380038u, kMagic), 0x30003000u, 0xD800D800u);   // /8,  -128
-        e[2] = h2fma(lop3_and_or(p, 0x01C001C0u, kMagic), 0x24002400u, 0xCC00CC00u);   // /64, -16
-        e[3] = h2add(lop3_and_or(q, 0x00070007u, kMagic), kNeg1024);
-        e[4] = h2fma(lop3_and_or(q, 0x00380038u, kMagic), 0x30003000u, 0xD800D800u);
+    __device__ static __forceinline__ void consts(uint32_t zz, uint32_t (&k)[kConsts]) {
+        k[0] = h2sub(0xE400E400u, zz);     // -(1024 + z)
+        k[1] = h2sub(0xD800D800u, zz);     // -(128 + z)
+        k[2] = h2sub(0xCC00CC00u, zz);     // -(16 + z)
     }
-    __device__ static __forceinline__ void run(const uint32_t (&w)[3], uint32_t (&e)[16]) {
+    __device__ static __forceinline__ void five(uint32_t p, const uint32_t (&k)[kConsts], uint32_t* e) {
+        const uint32_t q = p >> 9;
+        e[0] = h2add(lop3_and_or(p, 0x00070007u, kMagic), k[0]);
+        e[1] = h2fma(lop3_and_or(p, 0x00380038u, kMagic), 0x30003000u, k[1]);   // * 1/8
+        e[2] = h2fma(lop3_and_or(p, 0x01C001C0u, kMagic), 0x24002400u, k[2]);   // * 1/64
+        e[3] = h2add(lop3_and_or(q, 0x00070007u, kMagic), k[0]);
+        e[4] = h2fma(lop3_and_or(q, 0x00380038u, kMagic), 0x30003000u, k[1]);
+    }
+    __device__ static __forceinline__ void run(const uint32_t (&w)[3], const uint32_t (&k)[kConsts], uint32_t (&e)[16]) {
         // stream bits [s, s+16) of the first half next to bits [48+s, 48+s+16) of the second half
         const uint32_t l1 = __funnelshift_r(w[0], w[1], 15), l2 = __funnelshift_r(w[0], w[1], 30);
         const uint32_t u0 = __funnelshift_r(w[1], w[2], 16), u1 = __funnelshift_r(w[1], w[2], 31), u2 = w[2] >> 14;
-        five(__byte_perm(w[0], u0, 0x5410), e);
-        five(__byte_perm(l1, u1, 0x5410), e + 5);
-        five(__byte_perm(l2, u2, 0x5410), e + 10);
+        five(__byte_perm(w[0], u0, 0x5410), k, e);
+        five(__byte_perm(l1, u1, 0x5410), k, e + 5);
+        five(__byte_perm(l2, u2, 0x5410), k, e + 10);
         const uint32_t last = __byte_perm(w[1] >> 13, w[2] >> 29, 0x5410);               // codes 15 and 31
-        e[15] = h2add(lop3_and_or(last, 0x00070007u, kMagic), kNeg1024);
+        e[15] = h2add(lop3_and_or(last, 0x00070007u, kMagic), k[0]);
     }
 };
 
-template <int BITS> __device__ __forceinline__ void lds_chunk(uint32_t addr, uint32_t (&w)[BITS]) {
-    if constexpr (BITS == 4)
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
-    else if constexpr (BITS == 2)
-        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(addr));
-    else {
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(addr));
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[1]) : "r"(addr + 4));
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[2]) : "r"(addr + 8));
+// One chunk (BITS words) from shared memory with the widest load its alignment allows.
+template <int BITS> __device__ __forceinline__ void lds_chunk(const unsigned char* p, uint32_t (&w)[BITS]) {
+    if constexpr (BITS == 4) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    } else if constexpr (BITS == 2) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        w[0] = v.x; w[1] = v.y;
+    } else {
+        const uint32_t* q = reinterpret_cast<const uint32_t*>(p);
+        w[0] = q[0]; w[1] = q[1]; w[2] = q[2];
     }
 }
 
-// Even split of n items into parts: start of part i.
-__device__ __host__ __forceinline__ int part_begin(int n, int parts, int i) { return (int)(((long long)n * i) / parts); }
+// Even split of n items into `parts`: part i starts at i*q + min(i, r) with q = n / parts, r = n % parts
+// (q and r come from the host, so the kernel does no division on its way to the first copy).
+__device__ __forceinline__ int split_begin(int i, int q, int r) { return i * q + min(i, r); }
 
 template <int BITS>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
     extern __shared__ __align__(128) unsigned char smem[];
+    // The next kernel of the stream may start right away: it only prefetches its own weights until
+    // this grid has completed.
+    asm volatile("griddepcontrol.launch_dependents;");
+    CB_STAMP(0);
     const GemvParams& P = S.g;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -183,31 +244,33 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
     constexpr int kGroupBytes = 4 * kChunkBytes;     // one 128-code group
 
     // ---- this CTA's share: K-partition `split`, row slab `slab`
-    const int split = blockIdx.x % P.split_k, slab = blockIdx.x / P.split_k;
-    const int g_begin = part_begin(P.groups, P.split_k, split), g_end = part_begin(P.groups, P.split_k, split + 1);
-    const int ng = g_end - g_begin;
-    const int vpairs = (P.V + 1) >> 1;
-    const int row_begin = 2 * part_begin(vpairs, S.nslabs, slab);
-    const int row_end = min(P.V, 2 * part_begin(vpairs, S.nslabs, slab + 1));
+    int split = 0, slab = blockIdx.x;
+    if (P.split_k > 1) { split = blockIdx.x % P.split_k; slab = blockIdx.x / P.split_k; }
+    const int g_begin = 2 * split_begin(split, S.grp_q, S.grp_r);
+    const int ng = 2 * split_begin(split + 1, S.grp_q, S.grp_r) - g_begin;
+    const int row_begin = 2 * split_begin(slab, S.pair_q, S.pair_r);
+    const int row_end = min(P.V, 2 * split_begin(slab + 1, S.pair_q, S.pair_r));
     const int npass = (row_end - row_begin + kRowsPerPass - 1) / kRowsPerPass;
     const uint32_t row_bytes = (uint32_t)ng * kGroupBytes;
 
     const uint32_t s_base = smem_u32(smem);
-    const uint32_t s_ring = s_base + S.off_ring, s_bar = s_base + S.off_bar, s_x = s_base + S.off_x;
-    float* xsum = reinterpret_cast<float*>(smem + S.off_xsum);       // [ng][8]
+    const uint32_t s_ring = s_base + S.off_ring, s_bar = s_base + S.off_bar;
     float* red = reinterpret_cast<float*>(smem + S.off_red);         // [2][warps][2 tiles][32 lanes][4]
 
     if (tid == 0) {
-        for (int b = 0; b < S.nbuf; ++b) mbar_init(s_bar + 8 * b, 1);
+        for (int b = 0; b < S.nbuf; ++b) mbar_init(s_bar + 8 * b, 33);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    // Issue the row copies of pass `p` into ring slot p % nbuf (warp 0, one row per lane).
+    // Issue the copies of pass `p` into ring slot p % nbuf (warp 0, one row per lane): the packed row
+    // with one bulk copy, its scales and zeros with 4-byte cp.async.  The slot's mbarrier completes
+    // after the expect-tx arrival, the bulk bytes, and one arrival per lane once its cp.async landed.
     auto issue_pass = [&](int p) {
         const int buf = p % S.nbuf;
         const int row0 = row_begin + p * kRowsPerPass;
         const int nrows = min(kRowsPerPass, row_end - row0);
+        const uint32_t slot = s_ring + (uint32_t)buf * S.slot_bytes;
         const uint32_t bar = s_bar + 8 * buf;
         if (lane == 0) mbar_expect_tx(bar, (uint32_t)nrows * row_bytes);
         __syncwarp();
@@ -216,99 +279,61 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
             map_row(P, row0 + lane, proj, lr);
             const unsigned char* src = reinterpret_cast<const unsigned char*>(P.p[proj].w) +
                                        ((size_t)lr * P.wpr * 4 + (size_t)g_begin * kGroupBytes);
-            bulk_g2s(s_ring + (uint32_t)buf * (kRowsPerPass * S.pitch) + (uint32_t)lane * S.pitch, src, row_bytes, bar);
+            bulk_g2s(slot + (uint32_t)lane * S.pitch, src, row_bytes, bar);
+            const __half* ssrc = reinterpret_cast<const __half*>(P.p[proj].s) + (size_t)lr * P.groups + g_begin;
+            const __half* zsrc = reinterpret_cast<const __half*>(P.p[proj].z) + (size_t)lr * P.groups + g_begin;
+            const uint32_t sdst = slot + kRowsPerPass * S.pitch + (uint32_t)lane * S.meta_stride;
+            const uint32_t zdst = sdst + kRowsPerPass * S.meta_stride;
+            for (int j = 0; j < ng; j += 2) {
+                cp_async4(sdst + 2 * j, ssrc + j);
+                cp_async4(zdst + 2 * j, zsrc + j);
+            }
         }
+        cp_async_arrive_noinc(bar);
     };
     if (warp == 0) {
         for (int p = 0; p < min(npass, S.nbuf); ++p) issue_pass(p);
     }
-    // Let the next kernel of the stream start its own weight copies, then wait until everything the
-    // previous kernel wrote (our activations, the scratch) is visible.
-    asm volatile("griddepcontrol.launch_dependents;");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    // ---- stage activations as MMA B fragments: xfrag[b][group][i][t] = 16 bytes = e-order pairs 4i..4i+3
-    // of chunk t of the group; xsum[group][b] = sum of the 128 activations.
-    const int nitems = S.bpad * ng * 4;
-    for (int base = 0; base < nitems; base += kThreads) {      // whole warps stay in the loop: it shuffles
-        const int item = base + tid;
-        const bool live = item < nitems;
-        const int c = item & 3, gl = live ? (item >> 2) % ng : 0, b = live ? (item >> 2) / ng : 0;
-        float sum = 0.f;
-        uint32_t out[16];
-#pragma unroll
-        for (int m = 0; m < 16; ++m) out[m] = 0u;
-        if (live && b < P.B) {
-            const __half* src = x + (size_t)b * P.K + (size_t)(g_begin + gl) * 128 + c * 32;
-            __half v[32];
-            const uint4* s4 = reinterpret_cast<const uint4*>(src);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(v)[i] = __ldg(s4 + i);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) sum += __half2float(v[j]);
-#pragma unroll
-            for (int m = 0; m < 16; ++m) {
-                const int lo = Unpack<BITS>::pair_lo(m);
-                const __half2 pr = __halves2half2(v[lo], v[lo + Unpack<BITS>::pair_gap()]);
-                out[m] = *reinterpret_cast<const uint32_t*>(&pr);
-            }
-        }
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if (live) {
-            unsigned char* dst = smem + S.off_x + (size_t)b * S.xb_stride + (size_t)gl * 256;
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                *reinterpret_cast<uint4*>(dst + (i * 4 + c) * 16) =
-                    make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
-            if (c == 0) xsum[gl * 8 + b] = sum;
-        }
-    }
-    // zero the sums of batch rows that do not exist (the epilogue math reads all eight)
-    for (int i = tid; i < ng * 8; i += kThreads)
-        if ((i & 7) >= S.bpad) xsum[i] = 0.f;
-    __syncthreads();
+    CB_STAMP(1);
 
     // ---- this warp's groups inside the K-partition
-    const int wg_begin = part_begin(ng, kWarps, warp), wg_end = part_begin(ng, kWarps, warp + 1);
+    const int wg_begin = (ng * warp) >> 3, wg_end = (ng * (warp + 1)) >> 3;
+
+    // Wait until everything the previous kernel wrote (our activations, the scratch) is visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    CB_STAMP(2);
+
     const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool has_x = g < S.bpad;
+    // Lane (g, t) supplies the MMA B fragments of batch row g: the 32 activations of chunk t of each
+    // group, read straight from global memory one group ahead of their use (the vector is small and
+    // stays in L1/L2; staging it in shared memory would cost a CTA-wide barrier).
+    const bool has_x = g < P.B;
+    const __half* xrow = x + (size_t)(has_x ? g : 0) * P.K + (size_t)g_begin * 128 + t * 32;
+    auto load_x = [&](int gl, uint32_t (&r)[16]) {
+        if (has_x && gl < wg_end) {
+            const uint4* xp = reinterpret_cast<const uint4*>(xrow + (size_t)gl * 128);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = __ldg(xp + i);
+                r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = 0u;
+        }
+    };
+    uint32_t xnext[16];
+    load_x(wg_begin, xnext);
     int failed = 0;
+    CB_STAMP(3);
 
     for (int p = 0; p < npass; ++p) {
         const int buf = p % S.nbuf;
         const int row0 = row_begin + p * kRowsPerPass;
         const uint32_t parity = (uint32_t)((p / S.nbuf) & 1);
-        // scale/zero rows of this thread: rows g and g+8 of both tiles
-        const __half* sp[4];
-        const __half* zp[4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int v = row0 + (r >> 1) * 16 + (r & 1) * 8 + g;
-            int proj = 0, lr = 0;
-            if (v < row_end) map_row(P, v, proj, lr);
-            const bool ok = v < row_end;
-            sp[r] = ok ? reinterpret_cast<const __half*>(P.p[proj].s) + (size_t)lr * P.groups + g_begin : nullptr;
-            zp[r] = ok ? reinterpret_cast<const __half*>(P.p[proj].z) + (size_t)lr * P.groups + g_begin : nullptr;
-        }
-        float acc[2][4];
-#pragma unroll
-        for (int i = 0; i < 2; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-
-        // first group's metadata goes out before we block on the weights
-        float sc[4], sz[4];
-        auto load_meta = [&](int gl) {
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                float s = 0.f, z = 0.f;
-                if (sp[r] != nullptr && gl < wg_end) { s = __half2float(__ldg(sp[r] + gl)); z = __half2float(__ldg(zp[r] + gl)); }
-                sc[r] = s; sz[r] = -s * z;
-            }
-        };
-        load_meta(wg_begin);
-
+        const int ntile = (min(kRowsPerPass, row_end - row0) + 15) >> 4;
+        const unsigned char* rbase = smem + S.off_ring + (size_t)buf * S.slot_bytes;
+        float* myred = red + (size_t)(p & 1) * (kWarps * 2 * 32 * 4);
         {   // bounded wait for this pass's rows
             int spins = 0;
             const uint32_t bar = s_bar + 8 * buf;
@@ -316,55 +341,66 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
                 if (++spins > kSpinLimit) { failed = p + 1; break; }
             }
         }
-        const int ntile = (min(kRowsPerPass, row_end - row0) + 15) >> 4;
-        const uint32_t rbase = s_ring + (uint32_t)buf * (kRowsPerPass * S.pitch);
+        if (p == 0) CB_STAMP(4);
+        float acc[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
         for (int gl = wg_begin; gl < wg_end; ++gl) {
-            float cs[4], cz[4];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) { cs[r] = sc[r]; cz[r] = sz[r]; }
-            if (gl + 1 < wg_end) load_meta(gl + 1);
-            // activations of this group for batch row g
+            // activations of this group, re-paired to match the unpack order; the next group's are requested now
             uint32_t xf[16];
-            if (has_x) {
-                const uint32_t xa = s_x + (uint32_t)g * S.xb_stride + (uint32_t)gl * 256 + (uint32_t)t * 16;
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(xf[4 * i]), "=r"(xf[4 * i + 1]), "=r"(xf[4 * i + 2]), "=r"(xf[4 * i + 3]) : "r"(xa + i * 64));
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) xf[i] = 0u;
+            for (int m = 0; m < 16; ++m) {
+                const int lo = Unpack<BITS>::pair_lo(m), hi = lo + Unpack<BITS>::pair_gap();
+                xf[m] = __byte_perm(xnext[lo >> 1], xnext[hi >> 1], (lo & 1) ? 0x7632 : 0x5410);
             }
-            const float2 xs = *reinterpret_cast<const float2*>(&xsum[gl * 8 + 2 * t]);
+            load_x(gl + 1 < wg_end ? gl + 1 : wg_begin, xnext);      // wraps to the first group for the next pass
 #pragma unroll
             for (int tile = 0; tile < 2; ++tile) {
                 if (tile < ntile) {
+                    const unsigned char* arow = rbase + (size_t)(tile * 16 + g) * S.pitch + (size_t)gl * kGroupBytes + (size_t)t * kChunkBytes;
+                    const __half* s0 = reinterpret_cast<const __half*>(rbase + kRowsPerPass * S.pitch + (size_t)(tile * 16 + g) * S.meta_stride);
+                    const __half* s1 = s0 + 4 * S.meta_stride;                       // 8 rows further (stride is in bytes, pointer in halves)
+                    const __half* z0 = s0 + (kRowsPerPass / 2) * S.meta_stride;      // the zeros follow the 32 scale rows
+                    const __half* z1 = z0 + 4 * S.meta_stride;
+                    // rows past the end of the slab were never copied: give them scale 0 and a finite zero point
+                    const bool ok0 = row0 + tile * 16 + g < row_end, ok1 = row0 + tile * 16 + g + 8 < row_end;
+                    const float cs0 = ok0 ? __half2float(s0[gl]) : 0.f, cs1 = ok1 ? __half2float(s1[gl]) : 0.f;
+                    const uint32_t zr0 = ok0 ? (uint32_t)reinterpret_cast<const unsigned short*>(z0)[gl] : 0u;
+                    const uint32_t zr1 = ok1 ? (uint32_t)reinterpret_cast<const unsigned short*>(z1)[gl] : 0u;
+                    uint32_t ka[Unpack<BITS>::kConsts], kb[Unpack<BITS>::kConsts];
+                    Unpack<BITS>::consts(zr0 | (zr0 << 16), ka);
+                    Unpack<BITS>::consts(zr1 | (zr1 << 16), kb);
                     uint32_t wa[BITS], wb[BITS], ea[16], eb[16];
-                    const uint32_t a_addr = rbase + (uint32_t)(tile * 16 + g) * S.pitch + (uint32_t)gl * kGroupBytes + (uint32_t)t * kChunkBytes;
-                    lds_chunk<BITS>(a_addr, wa);
-                    lds_chunk<BITS>(a_addr + 8u * S.pitch, wb);
-                    Unpack<BITS>::run(wa, ea);
-                    Unpack<BITS>::run(wb, eb);
-                    float d[4];
-                    mma16816(d, ea[0], eb[0], ea[1], eb[1], xf[0], xf[1], zero4);
+                    lds_chunk<BITS>(arow, wa);
+                    lds_chunk<BITS>(arow + 8 * (size_t)S.pitch, wb);
+                    Unpack<BITS>::run(wa, ka, ea);
+                    Unpack<BITS>::run(wb, kb, eb);
+                    // two independent accumulation chains (even / odd k-steps)
+                    float d0[4], d1[4];
+                    mma16816(d0, ea[0], eb[0], ea[1], eb[1], xf[0], xf[1], zero4);
+                    mma16816(d1, ea[2], eb[2], ea[3], eb[3], xf[2], xf[3], zero4);
 #pragma unroll
-                    for (int m = 1; m < 8; ++m) mma16816(d, ea[2 * m], eb[2 * m], ea[2 * m + 1], eb[2 * m + 1], xf[2 * m], xf[2 * m + 1], d);
-                    // acc += s*D - (s*z)*sum(x): rows g (d0,d1) and g+8 (d2,d3), batch columns 2t, 2t+1
-                    acc[tile][0] = fmaf(cs[2 * tile], d[0], fmaf(cz[2 * tile], xs.x, acc[tile][0]));
-                    acc[tile][1] = fmaf(cs[2 * tile], d[1], fmaf(cz[2 * tile], xs.y, acc[tile][1]));
-                    acc[tile][2] = fmaf(cs[2 * tile + 1], d[2], fmaf(cz[2 * tile + 1], xs.x, acc[tile][2]));
-                    acc[tile][3] = fmaf(cs[2 * tile + 1], d[3], fmaf(cz[2 * tile + 1], xs.y, acc[tile][3]));
+                    for (int m = 2; m < 8; m += 2) {
+                        mma16816(d0, ea[2 * m], eb[2 * m], ea[2 * m + 1], eb[2 * m + 1], xf[2 * m], xf[2 * m + 1], d0);
+                        mma16816(d1, ea[2 * m + 2], eb[2 * m + 2], ea[2 * m + 3], eb[2 * m + 3], xf[2 * m + 2], xf[2 * m + 3], d1);
+                    }
+                    // acc += s * sum((q - z) x): rows g (d[0], d[1]) and g+8 (d[2], d[3]), batch columns 2t, 2t+1
+                    acc[tile][0] = fmaf(cs0, d0[0] + d1[0], acc[tile][0]);
+                    acc[tile][1] = fmaf(cs0, d0[1] + d1[1], acc[tile][1]);
+                    acc[tile][2] = fmaf(cs1, d0[2] + d1[2], acc[tile][2]);
+                    acc[tile][3] = fmaf(cs1, d0[3] + d1[3], acc[tile][3]);
                 }
             }
         }
-
-        // ---- meet the other warps (they covered other groups of the same rows)
-        float* myred = red + (size_t)(p & 1) * (kWarps * 2 * 32 * 4);
+        // ---- hand the partial sums to the reduction (other warps covered other groups)
 #pragma unroll
         for (int tile = 0; tile < 2; ++tile)
             *reinterpret_cast<float4*>(&myred[((warp * 2 + tile) * 32 + lane) * 4]) =
                 make_float4(acc[tile][0], acc[tile][1], acc[tile][2], acc[tile][3]);
+        if (p == 0) CB_STAMP(5);
         __syncthreads();
         // the ring slot is free again: refill it with pass p + nbuf
         if (warp == 0 && p + S.nbuf < npass) {
@@ -389,6 +425,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
             }
         }
     }
+    CB_STAMP(6);
     if (failed) atomicExch(&g_stream_status, failed);
 
     if (P.split_k > 1) {
@@ -424,29 +461,31 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
     const int sms = sm_count_current();
     if (sms <= 0) return CB_ERR_CUDA;
     StreamParams S{};
-    // K-partitions: the caller's split_k in units of groups, raised if the x fragments of one
-    // partition would not fit beside the weight ring.
-    int split = std::max(1, std::min(P.split_k, P.groups));
-    const int bpad = P.B <= 1 ? 1 : (P.B <= 2 ? 2 : (P.B <= 4 ? 4 : 8));
+    // K-partitions are whole PAIRS of groups (4-byte granularity of the metadata copies); the caller's
+    // split_k is raised if the activations of one partition would not fit beside the weight ring.
+    const int gpairs = P.groups / 2;
+    int split = std::max(1, std::min(P.split_k, gpairs));
     const int group_bytes = 16 * BITS;
     auto layout = [&](int sp, int nbuf, StreamParams& out) -> size_t {
-        const int ng = (P.groups + sp - 1) / sp;                      // largest partition
+        const int ng = 2 * ((gpairs + sp - 1) / sp);                  // largest partition
+        int meta = ng * 2;
+        meta += ((4 - meta) % 128 + 128) % 128;                        // rows 4 bytes apart (mod 128): conflict-free 2-byte reads
         int pitch = ng * group_bytes;
         pitch += ((group_bytes - pitch) % 128 + 128) % 128;           // pitch == group_bytes (mod 128): conflict-free fragment reads
         int xb = ng * 256;
         xb += ((64 - xb) % 128 + 128) % 128;                          // batch rows 64 bytes apart (mod 128)
         size_t off = 0;
-        out.off_bar = (unsigned)off; off += 64;
-        out.off_xsum = (unsigned)off; off += (size_t)ng * 8 * sizeof(float);
+        out.off_bar = (unsigned)off; off += 64;                      // 2 mbarriers per ring slot, at most 3 slots
         off = (off + 127) & ~(size_t)127;
         out.off_red = (unsigned)off; off += (size_t)2 * kWarps * 2 * 32 * 4 * sizeof(float);
-        out.off_x = (unsigned)off; off += (size_t)bpad * xb;
+        out.off_x = 0;
         off = (off + 127) & ~(size_t)127;
-        out.off_ring = (unsigned)off; off += (size_t)nbuf * kRowsPerPass * pitch;
-        out.pitch = pitch; out.xb_stride = xb; out.nbuf = nbuf; out.bpad = bpad;
+        out.slot_bytes = kRowsPerPass * (pitch + 2 * meta);
+        out.off_ring = (unsigned)off; off += (size_t)nbuf * out.slot_bytes;
+        out.pitch = pitch; out.meta_stride = meta; out.xb_stride = xb; out.nbuf = nbuf;
         return off;
     };
-    while (layout(split, 1, S) > kSmemCap && split < P.groups) ++split;
+    while (layout(split, 1, S) > kSmemCap && split < gpairs) ++split;
     if (layout(split, 1, S) > kSmemCap) return -1;
     // scratch: [65536 counters | split x B x V partial sums]; without enough of it this path is not taken
     constexpr size_t kCounterBytes = 65536 * sizeof(int);
@@ -469,6 +508,8 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
     P.split_k = split;
     S.g = P;
     S.nslabs = nslabs;
+    S.pair_q = vpairs / nslabs; S.pair_r = vpairs % nslabs;
+    S.grp_q = gpairs / split; S.grp_r = gpairs % split;
 
     static bool attr_done[64] = {};     // per device: the opt-in to large dynamic shared memory
     auto kern = gemv_stream_kernel<BITS>;
@@ -498,7 +539,7 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
 // the kernel's domain (the caller then uses the generic kernel).
 int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, int64_t rho, bool pdl,
                        void* scratch, size_t scratch_bytes, cudaStream_t stream) {
-    if (dtype != CB_F16 || P.group_size != 128 || P.K % 128 != 0 || P.B > kMaxBatchBlock || P.B < 1) return -1;
+    if (dtype != CB_F16 || P.group_size != 128 || P.K % 256 != 0 || P.B > kMaxBatchBlock || P.B < 1) return -1;
     if (reinterpret_cast<uintptr_t>(x) % 16 != 0) return -1;
     for (int i = 0; i < 3; ++i)
         if (reinterpret_cast<uintptr_t>(P.p[i].w) % 16 != 0) return -1;
@@ -517,6 +558,14 @@ int stream_status_read_and_clear(int* out) {
     *out = v;
     return CB_OK;
 }
+
+#ifdef CB_STREAM_TIMING
+}  // namespace cb
+extern "C" int cb_debug_stream_times(unsigned long long* host, int ctas) {
+    return (int)cudaMemcpyFromSymbol(host, cb::g_stream_times, sizeof(unsigned long long) * 8 * ctas);
+}
+namespace cb {
+#endif
 
 int occupancy_gemv_stream(int bits) {
     (void)bits;
