@@ -133,8 +133,10 @@ size_t cb_gemv_scratch_bytes(int64_t B, int64_t V, int64_t split_k);
 void cb_set_option(int option, int value);
 
 /* Synchronises the device, then returns in *status the decode kernels' error word and clears it:
- * 0 = no problem; k > 0 = a shared-memory copy of pass k-1 did not arrive within the wait limit and
- * the affected outputs were not written.  No counterpart in the reference. */
+ * 0 = no problem; 0 < k < 1000 = in a decode kernel a shared-memory copy of pass k-1 did not arrive
+ * within the wait limit and the affected outputs were not written; 1000 + r = in the tensor-core GEMM
+ * role r (1 TMA producer, 2 MMA issuer, 3 dequantiser, 4 epilogue) gave up a bounded wait.  No
+ * counterpart in the reference. */
 int cb_decode_status(int* status);
 
 /* Introspection used by the Split-K policy (packed_gemv.cu:339-347; bindings.cpp:37-39). */

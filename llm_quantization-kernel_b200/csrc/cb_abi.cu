@@ -39,6 +39,9 @@ int sm_count_current() {
 int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, int64_t rho, bool pdl,
                        void* scratch, size_t scratch_bytes, cudaStream_t stream);
 int stream_status_read_and_clear(int* out);
+int gemm_status_read_and_clear(int* out);
+int launch_gemm_tc(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
+                   int64_t gs, int act, cudaStream_t stream);
 
 // Programmatic dependent launch for the streamlined decode kernel (on unless CRISPYBITS_PDL=0).
 static int g_pdl = -1;
@@ -173,7 +176,13 @@ void cb_set_option(int option, int value) {
 
 int cb_decode_status(int* status) {
     if (status == nullptr) { set_error("cb_decode_status: NULL"); return CB_ERR_INVALID; }
-    return stream_status_read_and_clear(status);
+    int a = 0, b = 0;
+    int rc = stream_status_read_and_clear(&a);
+    if (rc != CB_OK) return rc;
+    rc = gemm_status_read_and_clear(&b);
+    if (rc != CB_OK) return rc;
+    *status = a != 0 ? a : (b != 0 ? 1000 + b : 0);
+    return CB_OK;
 }
 int cb_tile_n(void) { return kTileN; }
 
@@ -268,6 +277,11 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out, int6
     if (M == 0) return CB_OK;
     CB_REQUIRE(out != nullptr, "packed_gemm: out is NULL");
     CB_REQUIRE(M < (1ll << 30), "packed_gemm: M out of range");
+    if (use_tensor_cores && !g_force_generic) {
+        // tcgen05 kernel when the problem is inside its domain (-1 = it is not)
+        const int rc2 = launch_gemm_tc(dtype, x, M, w, out, K, bits, group_size, act, reinterpret_cast<cudaStream_t>(stream));
+        if (rc2 != -1) return rc2;
+    }
     const int round_w = (use_tensor_cores && dtype != CB_F32) ? 1 : 0;
     return launch_gemm_simt(dtype, x, M, w, out, K, bits, group_size, act, round_w,
                             reinterpret_cast<cudaStream_t>(stream));

@@ -378,15 +378,19 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
                     lds_chunk<BITS>(arow + 8 * (size_t)S.pitch, wb);
                     Unpack<BITS>::run(wa, ka, ea);
                     Unpack<BITS>::run(wb, kb, eb);
-                    // two independent accumulation chains (even / odd k-steps)
-                    float d0[4], d1[4];
+                    // Four independent accumulation chains of depth two: on this GPU a dependent mma.sync
+                    // issues ~110 cycles after its predecessor, so the eight k-steps must not form one chain.
+                    float d0[4], d1[4], d2[4], d3[4];
                     mma16816(d0, ea[0], eb[0], ea[1], eb[1], xf[0], xf[1], zero4);
                     mma16816(d1, ea[2], eb[2], ea[3], eb[3], xf[2], xf[3], zero4);
+                    mma16816(d2, ea[4], eb[4], ea[5], eb[5], xf[4], xf[5], zero4);
+                    mma16816(d3, ea[6], eb[6], ea[7], eb[7], xf[6], xf[7], zero4);
+                    mma16816(d0, ea[8], eb[8], ea[9], eb[9], xf[8], xf[9], d0);
+                    mma16816(d1, ea[10], eb[10], ea[11], eb[11], xf[10], xf[11], d1);
+                    mma16816(d2, ea[12], eb[12], ea[13], eb[13], xf[12], xf[13], d2);
+                    mma16816(d3, ea[14], eb[14], ea[15], eb[15], xf[14], xf[15], d3);
 #pragma unroll
-                    for (int m = 2; m < 8; m += 2) {
-                        mma16816(d0, ea[2 * m], eb[2 * m], ea[2 * m + 1], eb[2 * m + 1], xf[2 * m], xf[2 * m + 1], d0);
-                        mma16816(d1, ea[2 * m + 2], eb[2 * m + 2], ea[2 * m + 3], eb[2 * m + 3], xf[2 * m + 2], xf[2 * m + 3], d1);
-                    }
+                    for (int j = 0; j < 4; ++j) { d0[j] = (d0[j] + d1[j]) + (d2[j] + d3[j]); d1[j] = 0.f; }
                     // acc += s * sum((q - z) x): rows g (d[0], d[1]) and g+8 (d[2], d[3]), batch columns 2t, 2t+1
                     acc[tile][0] = fmaf(cs0, d0[0] + d1[0], acc[tile][0]);
                     acc[tile][1] = fmaf(cs0, d0[1] + d1[1], acc[tile][1]);

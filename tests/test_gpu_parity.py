@@ -260,6 +260,27 @@ def test_prefill_gemm(bits, M, act, dtype):
           TOL[torch.bfloat16] if dtype == torch.bfloat16 else 2e-3)
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("M,n,k", [(5, 256, 64), (130, 520, 1024), (300, 4096, 4096), (1024, 1000, 11008)])
+def test_prefill_gemm_tensor_core_kernel(bits, M, n, k):
+    """Shapes inside the tcgen05 kernel's domain (fp16, K a multiple of 64): parity with the
+    rounded-weight arithmetic of the reference's tensor-core path, ragged M and N tiles, bias, SiLU."""
+    from crispybits_kernels import _C, packed_linear
+    w, wd, bd = cached(n, k, bits, torch.float16, True, 9, 128, 0.02)
+    x = torch.randn(M, k, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(M))
+    y = packed_linear(x, w, act="silu", decode_threshold=0)
+    rounded = torch.nn.functional.silu(x.float() @ wd.half().float().T + bd)     # packed_gemm.cu:56,60
+    assert rel_err(y, rounded) < 1e-3
+    close(y, ref_linear(x, wd, bd, "silu"), torch.float16, 3e-3)                 # and the reference's bound vs fp32 weights
+    _C.set_option(1, 1)
+    try:
+        slow = packed_linear(x, w, act="silu", decode_threshold=0)               # CUDA-core kernel, same numerics
+    finally:
+        _C.set_option(1, 0)
+    assert rel_err(y, slow.float()) < 1e-3
+    assert _C.decode_status() == 0
+
+
 # ------------------------------------------------------------------ fused gate/up and QKV
 @pytest.mark.parametrize("bits", [2, 3, 4])
 @pytest.mark.parametrize("B", [1, 4])
