@@ -8,7 +8,7 @@
 // multiply by the scale rounds the exact product once, which is the same value as rounding the fp32
 // product.
 //
-// Shape of the kernel (one persistent CTA per SM, 15 warps, no cluster):
+// Shape of the kernel (one persistent CTA per SM, 23 warps, no cluster):
 //   tile        128 tokens (UMMA M) x 256 weight rows (UMMA N) x 64 codes per pipeline stage;
 //               tokens are the M side because the activation tile is what travels from L2 for every
 //               tile, and 128 x 64 fp16 is half of what a 256-token tile would cost; the packed
@@ -17,14 +17,14 @@
 //   warp 1      allocates TMEM, and one lane issues tcgen05.mma (kind::f16, 128x256x16, four per stage)
 //               with shared-memory descriptors; tcgen05.commit hands stages back and publishes finished
 //               accumulators.
-//   warps 2-9   dequantisers: one weight row per thread and stage.  The row's packed words are read from
+//   warps 2-17  dequantisers: half a weight row (32 codes) per thread and stage.  The row's packed words are read from
 //               a shared-memory ring, expanded with the (w & mask) | 0x6400 trick, and stored as fp16 in
 //               the K-major 128-byte-swizzled layout the MMA reads (16-byte chunk c of row r lands at
 //               chunk c ^ (r & 7)).
-//   warps 10-13 epilogue: tcgen05.ld of their 32 TMEM lanes (= 32 tokens), bias, activation, fp16, and
+//   warps 18-21 epilogue: tcgen05.ld of their 32 TMEM lanes (= 32 tokens), bias, activation, fp16, and
 //               64-byte row segments to global memory.  Two 256-column accumulators alternate, so the
 //               epilogue of one tile overlaps the main loop of the next.
-//   warp 14     TMA producer of the packed words: one 2-D box of 256 rows x 128 codes per two stages
+//   warp 22     TMA producer of the packed words: one 2-D box of 256 rows x 128 codes per two stages
 //               into a three-deep ring.  (Thread-per-row loads straight from global memory touch 32
 //               different cache lines per warp instruction and were measured to bound the whole
 //               pipeline; the bulk copy does the strided gather in the copy engine.)
@@ -41,8 +41,8 @@ namespace {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 3;
 constexpr int kPackedSlots = 3;                     // ring of packed super-blocks (128 codes = two stages each)
-constexpr int kThreads = 15 * 32;
-constexpr int kDequantWarps = 8, kFirstDequantWarp = 2, kFirstEpiWarp = 10, kPackedWarp = 14;
+constexpr int kThreads = 23 * 32;
+constexpr int kDequantWarps = 16, kFirstDequantWarp = 2, kFirstEpiWarp = 18, kPackedWarp = 22;
 constexpr uint32_t kXBytes = kBM * kBK * 2, kWBytes = kBN * kBK * 2;
 constexpr uint32_t kStageBytes = kXBytes + kWBytes;
 constexpr uint32_t kPackedSlotBytes = kBN * 64;     // 256 rows x 128 codes at 4 bits; narrower rows use less of it
@@ -111,20 +111,19 @@ __device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) {
 }
 constexpr uint32_t kMagic = 0x64006400u;
 
-// Dequantise the 64 codes of one row and stage into eight 16-byte chunks (8 consecutive fp16 each).
+// Dequantise 32 codes (BITS words) of one row into four 16-byte chunks (8 consecutive fp16 each).
 // Codes 2i, 2i+1 are taken together: both fields are masked in place from a copy of their byte(s),
 // (field | 0x6400) reads as 1024 + code * 2^p, one fused multiply-add with (2^-p) and
-// -(1024 * 2^-p + zero) leaves code - zero exactly, one multiply applies the scale.
-template <int BITS> struct RowDequant;
+// -(1024 * 2^-p + zero) leaves code - zero exactly, one multiply applies the scale.  The four steps of a
+// pair depend on each other; they are written stage by stage over eight pairs so that eight
+// independent chains are in flight.
+template <int BITS> struct Dequant32;
 
-// The four steps of a pair (byte permute, mask, fused multiply-add, multiply) depend on each other; they are
-// written stage by stage over eight pairs at a time so that eight independent chains are in flight.
-template <> struct RowDequant<4> {
-    static constexpr int kWords = 8;                 // 64 codes
-    __device__ static __forceinline__ void run(const uint32_t (&w)[kWords], uint32_t zz, uint32_t ss, uint4 (&chunk)[8]) {
+template <> struct Dequant32<4> {
+    __device__ static __forceinline__ void run(const uint32_t (&w)[4], uint32_t zz, uint32_t ss, uint4 (&chunk)[4]) {
         const uint32_t add = h2sub(0xD400E400u, zz);                 // (-1024 - z, -64 - z)
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {                             // word i = codes 8i..8i+7 = chunk i
+        for (int i = 0; i < 4; i += 2) {                             // word i = codes 8i..8i+7 = chunk i
             uint32_t t[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) t[j] = __byte_perm(w[i + (j >> 2)], 0u, (j & 3) | ((j & 3) << 8));   // byte -> bytes 0 and 2
@@ -140,13 +139,12 @@ template <> struct RowDequant<4> {
     }
 };
 
-template <> struct RowDequant<2> {
-    static constexpr int kWords = 4;
-    __device__ static __forceinline__ void run(const uint32_t (&w)[kWords], uint32_t zz, uint32_t ss, uint4 (&chunk)[8]) {
+template <> struct Dequant32<2> {
+    __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t zz, uint32_t ss, uint4 (&chunk)[4]) {
         const uint32_t add01 = h2sub(0xDC00E400u, zz);               // (-1024 - z, -256 - z)   fields at bits 0, 2
         const uint32_t add23 = h2sub(0xCC00D400u, zz);               // (-64 - z,  -16 - z)     fields at bits 4, 6
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {                                // word i = codes 16i..16i+15 = chunks 2i, 2i+1
+        for (int i = 0; i < 2; ++i) {                                // word i = codes 16i..16i+15 = chunks 2i, 2i+1
             uint32_t b[4], t[8];
 #pragma unroll
             for (int j = 0; j < 4; ++j) b[j] = __byte_perm(w[i], 0u, j | (j << 8));                           // byte j = codes 4j..4j+3
@@ -168,32 +166,28 @@ template <> struct RowDequant<2> {
     }
 };
 
-template <> struct RowDequant<3> {
-    static constexpr int kWords = 6;                 // two 96-bit chunks of 32 codes
-    __device__ static __forceinline__ void run(const uint32_t (&w)[kWords], uint32_t zz, uint32_t ss, uint4 (&chunk)[8]) {
+template <> struct Dequant32<3> {
+    __device__ static __forceinline__ void run(const uint32_t (&w)[3], uint32_t zz, uint32_t ss, uint4 (&chunk)[4]) {
         const uint32_t add = h2sub(0xE400E400u, zz);                 // (-1024 - z) twice
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {                                // 32 codes in words 3h..3h+2
+        for (int c = 0; c < 4; c += 2) {                             // 16 codes -> two chunks
+            uint32_t t[8];
 #pragma unroll
-            for (int c = 0; c < 4; c += 2) {                         // 16 codes -> two chunks
-                uint32_t t[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {                        // codes 2i, 2i+1 at stream bit 6i
-                    const int i = 4 * c + j, pos = 6 * i, wi = pos >> 5, off = pos & 31;
-                    if (off + 6 <= 32) t[j] = w[3 * h + wi] >> off;
-                    else t[j] = __funnelshift_r(w[3 * h + wi], w[3 * h + wi + 1], off);   // codes that straddle a word
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) t[j] = (t[j] & 0x3Fu) * 0x2001u;   // low code stays at bit 0, high code moves to bit 16
-#pragma unroll
-                for (int j = 0; j < 8; ++j) t[j] = lop3_and_or(t[j], 0x00070007u, kMagic);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) t[j] = h2fma(t[j], 0x3C003C00u, add);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) t[j] = h2mul(t[j], ss);
-                chunk[4 * h + c] = make_uint4(t[0], t[1], t[2], t[3]);
-                chunk[4 * h + c + 1] = make_uint4(t[4], t[5], t[6], t[7]);
+            for (int j = 0; j < 8; ++j) {                            // codes 2i, 2i+1 at stream bit 6i
+                const int i = 4 * c + j, pos = 6 * i, wi = pos >> 5, off = pos & 31;
+                if (off + 6 <= 32) t[j] = w[wi] >> off;
+                else t[j] = __funnelshift_r(w[wi], w[wi + 1], off);  // codes that straddle a word
             }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = (t[j] & 0x3Fu) * 0x2001u;   // low code stays at bit 0, high code moves to bit 16
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = lop3_and_or(t[j], 0x00070007u, kMagic);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = h2fma(t[j], 0x3C003C00u, add);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = h2mul(t[j], ss);
+            chunk[c] = make_uint4(t[0], t[1], t[2], t[3]);
+            chunk[c + 1] = make_uint4(t[4], t[5], t[6], t[7]);
         }
     }
 };
@@ -207,7 +201,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     unsigned char* smem = smem_raw + (base - raw);
     constexpr uint32_t kPackedOff = kStages * kStageBytes;
     constexpr uint32_t kBarOff = kPackedOff + kPackedSlots * kPackedSlotBytes;
-    constexpr int kWords = RowDequant<BITS>::kWords;                 // packed words of one row and stage
+    constexpr int kWords = 2 * BITS;                                 // packed words of one row and stage (64 codes)
     constexpr uint32_t kRowBytes = 2 * kWords * 4;                   // one row of a packed super-block (128 codes)
     const uint32_t s_bar = base + kBarOff;
     // barriers: full_x[s], full_w[s], empty[s], tmem_full[2], tmem_empty[2], full_p[slot], empty_p[slot]
@@ -309,8 +303,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             }
         }
     } else if (warp < kFirstEpiWarp) {
-        // ================= dequantisers: one weight row per thread and stage =================
-        const int r = (warp - kFirstDequantWarp) * 32 + lane;             // row of the 256-row tile
+        // ================= dequantisers: half a weight row (32 codes) per thread and stage =================
+        const int dq = (warp - kFirstDequantWarp) * 32 + lane;            // 0..511
+        const int r = dq & 255, kh = dq >> 8;                             // row of the 256-row tile, which 32-code half
         const uint32_t row_off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
         int it = 0, pit = 0;
         for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x) {
@@ -348,27 +343,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     const int s = it % kStages;
                     const uint32_t meta = half == 0 ? m0a : m0b;
                     const uint32_t ss = (meta & 0xFFFFu) * 0x10001u, zz = (meta >> 16) * 0x10001u;
-                    uint32_t w[kWords];
-                    const unsigned char* src = prow + half * (kWords * 4);
+                    uint32_t w[BITS];
+                    const unsigned char* src = prow + half * (kWords * 4) + kh * (BITS * 4);
                     if constexpr (BITS == 4) {
-                        const uint4 a = *reinterpret_cast<const uint4*>(src), b = *reinterpret_cast<const uint4*>(src + 16);
-                        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-                    } else if constexpr (BITS == 2) {
                         const uint4 a = *reinterpret_cast<const uint4*>(src);
                         w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+                    } else if constexpr (BITS == 2) {
+                        const uint2 a = *reinterpret_cast<const uint2*>(src);
+                        w[0] = a.x; w[1] = a.y;
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 3; ++i) {
-                            const uint2 a = *reinterpret_cast<const uint2*>(src + 8 * i);
-                            w[2 * i] = a.x; w[2 * i + 1] = a.y;
-                        }
+                        for (int i = 0; i < 3; ++i) w[i] = reinterpret_cast<const uint32_t*>(src)[i];
                     }
-                    uint4 chunk[8];
-                    RowDequant<BITS>::run(w, zz, ss, chunk);          // rows past N were zero-filled by the copy and get scale 0
+                    uint4 chunk[4];
+                    Dequant32<BITS>::run(w, zz, ss, chunk);           // rows past N were zero-filled by the copy and get scale 0
                     if (it >= kStages && !mbar_wait(empty(s), ((it / kStages) - 1) & 1, abort_flag)) { gave_up = 3; break; }
                     unsigned char* wtile = smem + s * kStageBytes + kXBytes + row_off;
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(wtile + ((c ^ (r & 7)) << 4)) = chunk[c];
+                    for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(wtile + (((4 * kh + c) ^ (r & 7)) << 4)) = chunk[c];
                     // make the generic-proxy writes visible to the tensor core's async-proxy reads, then signal
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
