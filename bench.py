@@ -42,12 +42,13 @@ import torch  # noqa: E402
 
 N_OUT, K_IN, GROUP = 4096, 4096, 128
 BITS = (4, 3, 2)
-COPIES = 16                 # distinct weight matrices per bit-width and step
+COPIES = 48                 # distinct weight matrices per bit-width and step (about 1 GB in all)
 FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 FALLBACK_TFLOPS = 1590.0
 METRIC = "packed W2/3/4 decode GEMV effective HBM bandwidth (4096x4096, group 128, batch 1)"
-# DRAM bytes per W4 4096x4096 launch from the committed ncu capture (profiles/); None until captured
-NCU_TRAFFIC_W4 = None
+METRIC_STACK = "packed mixed-precision decode stack effective HBM bandwidth (Llama-2-7B shapes, 32 blocks)"
+# dram__bytes_read + dram__bytes_write per W4 4096x4096 launch, from the ncu capture summarised under profiles/
+NCU_TRAFFIC_W4 = 8958464
 
 
 def gemv_bytes(n, k, bits, batch=1, group=GROUP):
@@ -93,14 +94,42 @@ def device_copies(d, device, copies):
 
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (read-only NVML
+    queries from a background thread every ~2 ms; falls back to an `nvidia-smi -lms` child process)."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.gpu, self.proc, self.path = gpu_index, None, None
+        self.thread, self.stop_flag, self.samples, self.mask, self.max_mhz = None, False, [], 0, None
+
+    def _nvml_loop(self, handle, nv):
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM))
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(handle))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.gpu).uuid)
+                handle = nv.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                handle = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(handle, nv), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -112,6 +141,14 @@ class ClockSampler:
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            if self.samples:
+                out.update(sm_mhz=float(statistics.median(self.samples)), sm_max_mhz=self.max_mhz,
+                           reasons=sorted(n for bit, n in self.REASONS.items() if self.mask & bit),
+                           samples=len(self.samples), source="nvml")
+            return out
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -134,7 +171,8 @@ class ClockSampler:
                     reasons.add(name)
         os.unlink(self.path)
         if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm),
+                       source="nvidia-smi")
         return out
 
 
@@ -250,7 +288,7 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
             outs.append([ck.packed_linear(x, w, workspace=ws) for w in weights[b]])
         graphs.append(gr)
 
-    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else 0)
+    sampler = ClockSampler(torch.cuda.current_device())
     if rank == 0:
         sampler.start()
     per_ms, total_ms = timed_graph_replays(graphs, args.steps, max(3, args.warmup), barrier)
@@ -319,6 +357,111 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
     }
 
 
+# ------------------------------------------------------------------ GPU arm: decode stack workload
+def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False):
+    """One step = the 128 packed decode launches of a Llama-2-7B-shaped 32-block stack (per-block bit-widths
+    from the seeded {2,3,4} draw), column-parallel over `world` GPUs with an all-gather after each launch."""
+    import crispybits_kernels as ck
+    from crispybits_kernels.stack import DecodeStack
+    hbm_peak, _, peak_kind = peaks()
+    batch = args.batch
+    st = DecodeStack(rank=rank, world=world, device=device)
+    g = torch.Generator().manual_seed(2)
+    x_host = torch.randn(batch, st.d_model, generator=g).half().pin_memory()
+    x = x_host.to(device)
+    for _ in range(2):
+        y = st.step(x)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y.float()).all(), "decode stack produced non-finite values"
+    graph, mode = None, "eager launches"
+    try:
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            st.step(x)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y = st.step(x)
+        graph.replay()
+        torch.cuda.synchronize()
+        mode = "CUDA graph replay of the whole step"
+    except Exception as exc:   # NCCL inside a capture is not available everywhere: time eager launches instead
+        graph = None
+        mode = f"eager launches (graph capture failed: {type(exc).__name__})"
+        torch.cuda.synchronize()
+
+    def one_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            st.step(x)
+
+    warm = max(3, args.warmup)
+    for _ in range(warm):
+        one_step()
+    sampler = ClockSampler(torch.cuda.current_device())
+    if rank == 0 and not sub:
+        sampler.start()
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        one_step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop() if (rank == 0 and not sub) else {}
+    total_ms = reduce_max(e0.elapsed_time(e1))
+    my_bytes = st.algorithmic_bytes(batch)
+    all_bytes = reduce_sum(float(my_bytes)) if world > 1 else float(my_bytes)
+    value = all_bytes * args.steps / (total_ms * 1e-3) / 1e9
+
+    y_host = torch.empty(batch, st.d_model, dtype=torch.float16).pin_memory()
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        one_step()
+        y_host.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3)
+    res = {
+        "metric": METRIC_STACK, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
+        "ms_per_step": total_ms / args.steps, "us_per_launch": total_ms * 1e3 / args.steps / st.launches_per_step(),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "decode_stack_llama2_7b_32blocks", "batch": batch, "bitmap_seed": 0,
+                   "mean_bits": float(np.mean(st.bitmap)), "parallelism": f"column-parallel N over {world} GPU(s), "
+                   "NCCL all-gather after each launch" if world > 1 else "single GPU",
+                   "l2": f"inputs larger than L2: {my_bytes / 1e6:.0f} MB of weights per rank and step", "launch": mode},
+        "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": value / world / hbm_peak, "traffic": None, "kernel": "decode step, per GPU",
+                     "algorithmic_bytes_per_launch": my_bytes / st.launches_per_step(), "peak_kind": f"of {peak_kind}"},
+        "e2e": {"value": all_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": batch * st.d_model * 2, "d2h_bytes_per_step": batch * st.d_model * 2,
+                "api": "DecodeStack.step: hidden state from pinned host memory, result copied back, every step"},
+        "cpu_baseline": None, "clocks": clocks, "gpu_launches": args.steps * st.launches_per_step(),
+    }
+    del st
+    torch.cuda.empty_cache()
+    return res
+
+
+_REDUCE_SUM = [None]
+
+
+def reduce_sum(v):
+    return _REDUCE_SUM[0](v) if _REDUCE_SUM[0] is not None else float(v)
+
+
 def bench_gemm(device, tf_peak, peak_kind, m=1024, iters=10):
     """Prefill GEMM at M=1024 over the 4096x4096 W4 and W3 matrices (TFLOP/s = 2*M*N*K / t)."""
     import crispybits_kernels as ck
@@ -351,6 +494,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "gemv", "stack"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM figures")
+    ap.add_argument("--no-stack", action="store_true", help="skip the 1-GPU decode-stack figures at N=1")
+    ap.add_argument("--batch", type=int, default=1, help="decode batch of the stack workload (1..8)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -381,7 +526,25 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    line = run_gemv_workload(args, rank, world, device, barrier, reduce_max)
+    def reduce_sum_impl(v):
+        if dist is None:
+            return float(v)
+        t = torch.tensor([float(v)], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    _REDUCE_SUM[0] = reduce_sum_impl
+    # N = 1: the 4096x4096 GEMVs the headline metric is quoted on (plus, as extra objects, the prefill GEMM
+    # and the 1-GPU decode stack).  N > 1: single matmuls stay on one GPU, so the path that shards -- the
+    # decode stack -- is what runs; the "stack" object of the N = 1 line is its 1-GPU point.
+    workload = args.workload or ("gemv" if world == 1 else "stack")
+    if workload == "stack":
+        line = run_stack_workload(args, rank, world, device, barrier, reduce_max)
+    else:
+        line = run_gemv_workload(args, rank, world, device, barrier, reduce_max)
+        if world == 1 and not args.no_stack:
+            sub = run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=True)
+            line["stack"] = {k: sub[k] for k in ("metric", "value", "unit", "ms_per_step", "us_per_launch", "config", "roofline", "e2e")}
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:

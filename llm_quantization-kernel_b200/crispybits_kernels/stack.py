@@ -1,0 +1,185 @@
+"""A Llama-2-7B-shaped mixed-precision decode stack made only of the packed linears, optionally split
+column-parallel on N over the GPUs of one node.
+
+This is the multi-GPU form of the packed linear path; the reference is single-GPU and has no
+counterpart.  Per transformer block the four decode launches are
+    fused QKV   [3*d/g rows  <- d]      (one launch, three outputs: the rank's Q, K and V heads)
+    o_proj      [d/g rows    <- d]
+    gate/up     [2*f/g rows  <- d]      (the fused silu(gate)*up kernel, f/g outputs)
+    down        [d/g rows    <- f]
+with d = 4096, f = 11008, every block at its own bit-width from {2, 3, 4}.  Every rank holds the
+rows [r*n/g, (r+1)*n/g) of each matrix (Q, K, V by whole heads; gate and up by the same rows) and
+the full activation; after each launch the [B, n/g] slice that the next launch consumes is
+all-gathered over NVLink, so that every rank again holds the full [B, n] activation (four gathers per
+block: Q, o_proj, gate/up, down; the K and V slices stay on their rank, as their consumer --
+attention -- is head-parallel).
+
+Only the linears and the gathers are in the step: attention, normalisation and residual adds of a
+real model are other kernels and are outside this path.  Each block reads the step's hidden state
+x; inside a block the data flows  x -> QKV -> (Q part) -> o_proj -> gate/up -> down.
+
+The synthetic weights are drawn on the GPU (seeded per block and matrix, identical on every rank) and
+quantised and packed there with plain torch operations that follow the reference's quantizer and
+bitstream bit for bit (Crispybits/Kernel/crispybits_kernels/reference.py:10-55); the tests check this
+against the CPU oracle.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .ops import PackedLinearWeight, fused_gate_up, fused_qkv, new_workspace, packed_linear
+
+LLAMA2_7B = dict(n_blocks=32, d_model=4096, d_ff=11008)
+
+
+def sample_bitmap(n_blocks: int = 32, seed: int = 0) -> List[int]:
+    """Seeded uniform draw of a per-block bit-width from {2, 3, 4}, the draw of the reference's
+    Crispybits/quantization/scripts/sample_bitmaps.py:11-12 (seed 0 gives mean 3.06 bits over 32 blocks)."""
+    rng = np.random.default_rng(seed)
+    return [int(b) for b in rng.choice(np.array([2, 3, 4], dtype=np.int8), size=n_blocks, replace=True)]
+
+
+# ------------------------------------------------------------------ quantise + pack with torch ops (any device)
+@torch.no_grad()
+def quantize_pack(w: torch.Tensor, bits: int, group_size: int = 128, dtype=torch.float16) -> PackedLinearWeight:
+    """Group-wise asymmetric affine quantisation and packing of a float32 [N, K] matrix on its device."""
+    assert bits in (2, 3, 4) and w.dim() == 2
+    n, k = w.shape
+    g = -(-k // group_size)
+    kp = g * group_size
+    wf = torch.zeros(n, kp, dtype=torch.float32, device=w.device)
+    wf[:, :k] = w.float()
+    if kp != k:
+        wf[:, k:] = wf[:, k - 1:k]
+    grp = wf.view(n, g, group_size)
+    qmax = float((1 << bits) - 1)
+    mn, mx = grp.amin(-1), grp.amax(-1)
+    scale = ((mx - mn) / qmax).clamp_min(1e-8)
+    zero = torch.round(-mn / scale).clamp(0, qmax)
+    q = torch.clamp(torch.round(grp / scale[..., None]) + zero[..., None], 0, qmax).view(n, kp)[:, :k].to(torch.int64)
+    c = -(-k // 32)
+    qq = torch.zeros(n, c * 32, dtype=torch.int64, device=w.device)
+    qq[:, :k] = q
+    qq = qq.view(n, c, 32)
+    words = torch.zeros(n, c, bits, dtype=torch.int64, device=w.device)
+    for j in range(32):                         # code j of a chunk sits at bit j*bits of the chunk's stream
+        wi, off = divmod(j * bits, 32)
+        v = qq[:, :, j] << off
+        words[:, :, wi] |= v & 0xFFFFFFFF
+        if off + bits > 32:
+            words[:, :, wi + 1] |= v >> 32
+    words = words.view(n, c * bits)
+    packed = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32).contiguous()
+    return PackedLinearWeight(packed, scale.to(dtype).contiguous(), zero.to(dtype).contiguous(), bits, group_size, k, n)
+
+
+def _rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = w.shape[0]
+    assert n % world == 0
+    return w[rank * n // world:(rank + 1) * n // world]
+
+
+@dataclass
+class _Block:
+    bits: int
+    q: PackedLinearWeight
+    k: PackedLinearWeight
+    v: PackedLinearWeight
+    o: PackedLinearWeight
+    gate: PackedLinearWeight
+    up: PackedLinearWeight
+    down: PackedLinearWeight
+
+
+class DecodeStack:
+    """The packed linears of `n_blocks` transformer blocks on one rank of a `world`-way column split."""
+
+    def __init__(self, n_blocks: int = 32, d_model: int = 4096, d_ff: int = 11008, bitmap: Optional[List[int]] = None,
+                 rank: int = 0, world: int = 1, device="cuda", seed: int = 0, std: float = 0.02, group_size: int = 128):
+        if d_model % world or d_ff % world or (d_model // world) % 2:
+            raise ValueError("d_model and d_ff must divide evenly over the ranks")
+        self.n_blocks, self.d_model, self.d_ff = n_blocks, d_model, d_ff
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.bitmap = list(bitmap) if bitmap is not None else sample_bitmap(n_blocks, seed)
+        if len(self.bitmap) != n_blocks:
+            raise ValueError("bitmap length does not match the number of blocks")
+        self.blocks: List[_Block] = []
+        self.workspace = new_workspace(self.device)
+        gen = torch.Generator(device=self.device)
+
+        def draw(block: int, which: int, n: int, k: int) -> torch.Tensor:
+            gen.manual_seed(1_000_003 * seed + 97 * block + which)       # same full matrix on every rank
+            return torch.randn(n, k, generator=gen, device=self.device, dtype=torch.float32) * std
+
+        for i, bits in enumerate(self.bitmap):
+            blk = _Block(
+                bits=bits,
+                q=quantize_pack(_rows(draw(i, 1, d_model, d_model), rank, world), bits, group_size),
+                k=quantize_pack(_rows(draw(i, 2, d_model, d_model), rank, world), bits, group_size),
+                v=quantize_pack(_rows(draw(i, 3, d_model, d_model), rank, world), bits, group_size),
+                o=quantize_pack(_rows(draw(i, 4, d_model, d_model), rank, world), bits, group_size),
+                gate=quantize_pack(_rows(draw(i, 5, d_ff, d_model), rank, world), bits, group_size),
+                up=quantize_pack(_rows(draw(i, 6, d_ff, d_model), rank, world), bits, group_size),
+                down=quantize_pack(_rows(draw(i, 7, d_model, d_ff), rank, world), bits, group_size))
+            self.blocks.append(blk)
+
+    # -------------------------------------------------------------- sizes
+    def algorithmic_bytes(self, batch: int) -> int:
+        """Bytes one rank must move per step: packed words + fp16 scales and zeros of its shards, plus the
+        activations read and written by its launches (weights counted once for any batch <= 8)."""
+        total = 0
+        for blk in self.blocks:
+            for w in (blk.q, blk.k, blk.v, blk.o, blk.gate, blk.up, blk.down):
+                total += w.packed.numel() * 4 + w.scales.numel() * 2 * 2
+            total += batch * 2 * (self.d_model + 3 * blk.q.out_features)         # QKV in / out
+            total += batch * 2 * (self.d_model + blk.o.out_features)
+            total += batch * 2 * (self.d_model + blk.gate.out_features)
+            total += batch * 2 * (self.d_ff + blk.down.out_features)
+        return total
+
+    def launches_per_step(self) -> int:
+        return 4 * self.n_blocks
+
+    # -------------------------------------------------------------- one decode step
+    def gather(self, t: torch.Tensor) -> torch.Tensor:
+        """[B, n/g] on every rank -> [B, n] on every rank.  NCCL all-gather over NVLink; the batch > 1 case
+        needs one transpose because the collective concatenates rank-major."""
+        if self.world == 1:
+            return t
+        import torch.distributed as dist
+        b, nl = t.shape
+        out = torch.empty(self.world * b, nl, dtype=t.dtype, device=t.device)      # rank-major rows
+        dist.all_gather_into_tensor(out, t.contiguous())
+        if b == 1:
+            return out.view(1, self.world * nl)
+        return out.view(self.world, b, nl).permute(1, 0, 2).reshape(b, self.world * nl)
+
+    def step(self, x: torch.Tensor, decode_threshold: int = 8) -> torch.Tensor:
+        """x [B, d_model] (replicated on every rank) -> the last block's down-projection output [B, d_model]."""
+        y = None
+        kw = dict(decode_threshold=decode_threshold, workspace=self.workspace)
+        for blk in self.blocks:
+            oq, _ok, _ov = fused_qkv(x, blk.q, blk.k, blk.v, **kw)
+            a = self.gather(packed_linear(self.gather(oq), blk.o, **kw))
+            m = self.gather(fused_gate_up(a, blk.gate, blk.up, **kw))
+            y = self.gather(packed_linear(m, blk.down, **kw))
+        return y                                          # the last block's output; every block ran the same launches
+
+    # -------------------------------------------------------------- check value (fp32, any device)
+    @torch.no_grad()
+    def reference_step(self, x: torch.Tensor, full_blocks: "List[Dict[str, torch.Tensor]]") -> torch.Tensor:
+        """fp32 evaluation of the same data flow from full (un-sharded) dequantised weights
+        {"q","k","v","o","gate","up","down"} per block; used by the tests."""
+        y = None
+        xf = x.float()
+        for wd in full_blocks:
+            q = xf @ wd["q"].T
+            a = (q.half().float()) @ wd["o"].T
+            a16 = a.half().float()
+            m = torch.nn.functional.silu(a16 @ wd["gate"].T) * (a16 @ wd["up"].T)
+            y = m.half().float() @ wd["down"].T
+        return y
