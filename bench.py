@@ -46,6 +46,12 @@ COPIES = 48                 # distinct weight matrices per bit-width and step (a
 FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 FALLBACK_TFLOPS = 1590.0
 METRIC = "packed W2/3/4 decode GEMV effective HBM bandwidth (4096x4096, group 128, batch 1)"
+COMM_TEXT = {
+    "nccl": "NCCL all-gather after each launch",
+    "p2p": "all-gather fused into the decode kernel: peer stores over NVLink and an in-kernel rank hand-shake",
+    "p2p_barrier": "all-gather fused into the decode kernel's epilogue as peer stores over NVLink, "
+                   "one-CTA flag barrier kernel (programmatic dependent launch) after each launch",
+}
 METRIC_STACK = "packed mixed-precision decode stack effective HBM bandwidth (Llama-2-7B shapes, 32 blocks)"
 # dram__bytes_read + dram__bytes_write per W4 4096x4096 launch, from the ncu capture summarised under profiles/
 NCU_TRAFFIC_W4 = 8958464
@@ -365,7 +371,7 @@ def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False
     from crispybits_kernels.stack import DecodeStack
     hbm_peak, _, peak_kind = peaks()
     batch = args.batch
-    st = DecodeStack(rank=rank, world=world, device=device)
+    st = DecodeStack(rank=rank, world=world, device=device, comm=args.comm)
     g = torch.Generator().manual_seed(2)
     x_host = torch.randn(batch, st.d_model, generator=g).half().pin_memory()
     x = x_host.to(device)
@@ -419,6 +425,8 @@ def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False
     all_bytes = reduce_sum(float(my_bytes)) if world > 1 else float(my_bytes)
     value = all_bytes * args.steps / (total_ms * 1e-3) / 1e9
 
+    if st.peer_status() != 0:
+        raise RuntimeError(f"rank {rank}: peer {st.peer_status() - 1} was not heard from in time")
     y_host = torch.empty(batch, st.d_model, dtype=torch.float16).pin_memory()
 
     def e2e_step():
@@ -439,8 +447,7 @@ def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False
         "ms_per_step": total_ms / args.steps, "us_per_launch": total_ms * 1e3 / args.steps / st.launches_per_step(),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "decode_stack_llama2_7b_32blocks", "batch": batch, "bitmap_seed": 0,
-                   "mean_bits": float(np.mean(st.bitmap)), "parallelism": f"column-parallel N over {world} GPU(s), "
-                   "NCCL all-gather after each launch" if world > 1 else "single GPU",
+                   "mean_bits": float(np.mean(st.bitmap)), "parallelism": (f"column-parallel N over {world} GPUs, " + COMM_TEXT[st.comm]) if world > 1 else "single GPU",
                    "l2": f"inputs larger than L2: {my_bytes / 1e6:.0f} MB of weights per rank and step", "launch": mode},
         "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
                      "frac": value / world / hbm_peak, "traffic": None, "kernel": "decode step, per GPU",
@@ -495,6 +502,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM figures")
     ap.add_argument("--no-stack", action="store_true", help="skip the 1-GPU decode-stack figures at N=1")
+    ap.add_argument("--comm", default="p2p_barrier", choices=["nccl", "p2p", "p2p_barrier"],
+                    help="how the column-parallel stack gathers its activations at N > 1")
     ap.add_argument("--batch", type=int, default=1, help="decode batch of the stack workload (1..8)")
     args = ap.parse_args()
 

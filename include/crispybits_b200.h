@@ -51,6 +51,35 @@ typedef struct cb_weight {
     int64_t n;             /* output rows            */
 } cb_weight;
 
+/* Where a decode launch of a column-parallel stack puts its output (no counterpart in the reference,
+ * which is single-GPU).  Output rows r < n_gather are stored to peer_out[p] + (b * ld + col + r) elements
+ * for every rank p < world (peer-mapped buffers of [B, ld] elements; the rank's own buffer included);
+ * rows r >= n_gather go to the ordinary `out` of the call.
+ *
+ * With sync != 0 the launch also carries the hand-shake between the ranks, so that no separate barrier
+ * is needed: before reading x it waits (bounded, about a second) until every peer has completed as many
+ * launches as this rank, and on completion it advances this rank's launch count and publishes it to all
+ * peers.  peer_flags[p] is rank p's flag array (world uint32, peer-mapped, zeroed once), my_flags this
+ * rank's own; epoch (uint32), done (int32) and status (int32) are zeroed words in this rank's memory:
+ * the launch count, the kernel's CTA counter, and 0 or 1 + the first peer not heard from in time (later
+ * waits then return at once).  Every rank must issue the same sequence of sync launches.  A launch may
+ * overwrite any gathered buffer except the one that launch itself reads on the peers (its x): when it
+ * stores, every peer has completed all earlier launches, so two alternating buffers are enough. */
+typedef struct cb_scatter {
+    void* peer_out[8];
+    int world;
+    int64_t n_gather;
+    int64_t ld;
+    int64_t col;
+    int sync;
+    int rank;
+    void* peer_flags[8];
+    void* my_flags;
+    void* epoch;
+    void* done;
+    int* status;
+} cb_scatter;
+
 /* Message of the last error raised on this thread ("" if none). */
 const char* cb_last_error(void);
 
@@ -86,6 +115,34 @@ int cb_fused_qkv(const void* x, int64_t B,
                  int64_t K, int bits, int64_t group_size, int dtype,
                  int64_t split_k, int64_t rho,
                  void* scratch, size_t scratch_bytes, void* stream);
+
+/* cb_packed_gemv / cb_fused_gate_up with the all-gather of a column-parallel stack fused into the
+ * epilogue: output rows named by `scatter` are written straight into every rank's gathered activation
+ * buffer (plain peer stores over NVLink).  scatter == NULL behaves like the plain entry point.  New for
+ * the multi-GPU decode stack; the reference has no multi-GPU code. */
+int cb_packed_gemv_scatter(const void* x, int64_t B, const cb_weight* w, void* out, const cb_scatter* scatter,
+                           int64_t K, int bits, int64_t group_size, int dtype,
+                           int64_t split_k, int64_t rho, int act,
+                           void* scratch, size_t scratch_bytes, void* stream);
+int cb_fused_gate_up_scatter(const void* x, int64_t B, const cb_weight* gate, const cb_weight* up, void* out,
+                             const cb_scatter* scatter, int64_t K, int bits, int64_t group_size, int dtype,
+                             int64_t split_k, int64_t rho,
+                             void* scratch, size_t scratch_bytes, void* stream);
+
+/* One-CTA barrier between the ranks of a column-parallel stack, to be launched on every rank after a
+ * scatter launch: tells every peer that this rank's launch is complete and waits (bounded, about a
+ * second) until every peer has said so.  peer_flags[p] is rank p's flag array (world uint32, zeroed
+ * once, peer-mapped), my_flags this rank's own, epoch a zeroed uint32 in this rank's memory that the
+ * kernel advances (graph replays keep counting), status a zeroed int that becomes 1 + p when peer p
+ * was not heard from in time (later barriers then return at once).  New for the multi-GPU stack. */
+int cb_peer_barrier(void* const* peer_flags, void* my_flags, void* epoch, int* status, int world, int rank,
+                    void* stream);
+
+/* Bounded wait, as a one-CTA kernel on `stream`, until every peer has completed as many hand-shake launches
+ * as this rank: what a consumer other than a hand-shake launch (a copy to the host, another library's kernel)
+ * needs before it reads a gathered buffer.  `scatter` supplies world, my_flags, epoch and status.  New for the
+ * multi-GPU stack. */
+int cb_peer_wait(const cb_scatter* scatter, void* stream);
 
 /* Prefill GEMM  out[M,n] = act(x[M,K] * Wdq^T + bias), float32 accumulation.
  * Replaces packed_gemm_cuda (Crispybits/Kernel/csrc/packed_gemm.cu:182-203; bindings.cpp:34).

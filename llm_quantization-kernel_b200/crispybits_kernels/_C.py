@@ -286,6 +286,105 @@ def fused_qkv(x, wq, sq, zq, bq, wk, sk, zk, bk, wv, sv, zv, bv, rope_cos, rope_
     return outs
 
 
+# ------------------------------------------------------------------ column-parallel stacks (no reference counterpart)
+class _Scatter(ctypes.Structure):
+    """struct cb_scatter of include/crispybits_b200.h"""
+    _fields_ = [("peer_out", _vp * 8), ("world", _int), ("n_gather", _i64), ("ld", _i64), ("col", _i64),
+                ("sync", _int), ("rank", _int), ("peer_flags", _vp * 8), ("my_flags", _vp), ("epoch", _vp),
+                ("done", _vp), ("status", _vp)]
+
+
+class PeerSync:
+    """Device words of the in-kernel rank hand-shake (see struct cb_scatter): peer flag arrays, own flag array,
+    launch count, CTA counter and status."""
+
+    def __init__(self, peer_flag_ptrs, my_flags: torch.Tensor, epoch: torch.Tensor, done: torch.Tensor,
+                 status: torch.Tensor, rank: int):
+        self.peer_flag_ptrs, self.rank = list(peer_flag_ptrs), int(rank)
+        self.my_flags, self.epoch, self.done, self.status = my_flags, epoch, done, status
+
+
+_SP = ctypes.POINTER(_Scatter)
+_lib.cb_packed_gemv_scatter.argtypes = [_vp, _i64, _WP, _vp, _SP, _i64, _int, _i64, _int, _i64, _i64, _int, _vp, _sz, _vp]
+_lib.cb_fused_gate_up_scatter.argtypes = [_vp, _i64, _WP, _WP, _vp, _SP, _i64, _int, _i64, _int, _i64, _i64, _vp, _sz, _vp]
+_lib.cb_peer_barrier.argtypes = [ctypes.POINTER(_vp), _vp, _vp, _vp, _int, _int, _vp]
+_lib.cb_peer_wait.argtypes = [_SP, _vp]
+for _f in ("cb_packed_gemv_scatter", "cb_fused_gate_up_scatter", "cb_peer_barrier", "cb_peer_wait"):
+    getattr(_lib, _f).restype = _int
+
+
+def _scatter(peer_ptrs, n_gather: int, ld: int, col: int, sync: "PeerSync | None" = None) -> _Scatter:
+    sc = _Scatter()
+    for i, ptr in enumerate(peer_ptrs):
+        sc.peer_out[i] = ptr
+    sc.world, sc.n_gather, sc.ld, sc.col = len(peer_ptrs), n_gather, ld, col
+    if sync is not None:
+        sc.sync, sc.rank = 1, sync.rank
+        for i, ptr in enumerate(sync.peer_flag_ptrs):
+            sc.peer_flags[i] = ptr
+        sc.my_flags, sc.epoch = sync.my_flags.data_ptr(), sync.epoch.data_ptr()
+        sc.done, sc.status = sync.done.data_ptr(), sync.status.data_ptr()
+    return sc
+
+
+def packed_gemv_scatter(x, packed, scales, zeros, bias, out, peer_ptrs, n_gather, ld, col, bits, in_features,
+                        group_size, split_k, rho, act, sync=None):
+    """packed_gemv whose output rows < n_gather go to every rank's gathered buffer (peer pointers) at column
+    `col` of a [B, ld] matrix; the other rows go to `out` [B, N]."""
+    bits, k, gs, split_k = int(bits), int(in_features), int(group_size), int(split_k)
+    _check_x(x, k)
+    _check_weight(x, packed, scales, zeros, bits, k, gs, "packed_gemv_scatter")
+    bias = _bias_or_none(bias, x, packed.shape[0])
+    B, n = x.shape[0], packed.shape[0]
+    if out.shape != (B, n) or out.dtype != x.dtype or not out.is_contiguous() or out.device != x.device:
+        _fail("packed_gemv_scatter: out must be a contiguous [B, N] tensor of x's dtype on x's device")
+    with torch.cuda.device(x.device):
+        st = _stream(x)
+        pk = max(1, min(split_k, -(-k // 32)))
+        sc = _decode_scratch(x, st, B, n, pk)
+        w, s = _weight(packed, scales, zeros, bias), _scatter(peer_ptrs, int(n_gather), int(ld), int(col), sync)
+        _rc(_lib.cb_packed_gemv_scatter(x.data_ptr(), B, ctypes.byref(w), out.data_ptr(), ctypes.byref(s), k, bits, gs,
+                                        _DTYPE[x.dtype], pk, int(rho), int(act), _ptr(sc), 0 if sc is None else sc.numel(), st))
+    return out
+
+
+def fused_gate_up_scatter(x, wg, sg, zg, wu, su, zu, out, peer_ptrs, n_gather, ld, col, bits, in_features, group_size,
+                          split_k, rho, sync=None):
+    bits, k, gs, split_k = int(bits), int(in_features), int(group_size), int(split_k)
+    _check_x(x, k)
+    _check_weight(x, wg, sg, zg, bits, k, gs, "fused_gate_up_scatter(gate)")
+    _check_weight(x, wu, su, zu, bits, k, gs, "fused_gate_up_scatter(up)")
+    if wg.shape != wu.shape:
+        _fail("gate/up packed shapes must match")
+    B, n = x.shape[0], wg.shape[0]
+    if out.shape != (B, n) or out.dtype != x.dtype or not out.is_contiguous():
+        _fail("fused_gate_up_scatter: out must be a contiguous [B, N] tensor of x's dtype")
+    with torch.cuda.device(x.device):
+        st = _stream(x)
+        pk = max(1, min(split_k, -(-k // 32)))
+        sc = _decode_scratch(x, st, B, 2 * n, pk)
+        g, u, s = _weight(wg, sg, zg, None), _weight(wu, su, zu, None), _scatter(peer_ptrs, int(n_gather), int(ld), int(col), sync)
+        _rc(_lib.cb_fused_gate_up_scatter(x.data_ptr(), B, ctypes.byref(g), ctypes.byref(u), out.data_ptr(), ctypes.byref(s),
+                                          k, bits, gs, _DTYPE[x.dtype], pk, int(rho), _ptr(sc), 0 if sc is None else sc.numel(), st))
+    return out
+
+
+def peer_barrier(peer_flag_ptrs, my_flags: torch.Tensor, epoch: torch.Tensor, status: torch.Tensor, rank: int):
+    """Launch the rank-to-rank barrier kernel on the current stream of my_flags' device."""
+    world = len(peer_flag_ptrs)
+    arr = (_vp * world)(*peer_flag_ptrs)
+    with torch.cuda.device(my_flags.device):
+        _rc(_lib.cb_peer_barrier(arr, my_flags.data_ptr(), epoch.data_ptr(), status.data_ptr(), world, int(rank),
+                                 torch.cuda.current_stream(my_flags.device).cuda_stream))
+
+
+def peer_wait(sync: "PeerSync"):
+    """Launch the bounded wait for the peers' latest hand-shake launch on the current stream."""
+    sc = _scatter([0] * len(sync.peer_flag_ptrs), 0, 1, 0, sync)
+    with torch.cuda.device(sync.my_flags.device):
+        _rc(_lib.cb_peer_wait(ctypes.byref(sc), torch.cuda.current_stream(sync.my_flags.device).cuda_stream))
+
+
 def unpack_codes(packed: torch.Tensor, bits: int, in_features: int) -> torch.Tensor:
     """int32 codes [N, K] from packed words, computed on the GPU (checked bit-for-bit in the tests)."""
     if not packed.is_cuda or packed.dtype != torch.int32 or packed.dim() != 2 or not packed.is_contiguous():

@@ -12,7 +12,12 @@ rows [r*n/g, (r+1)*n/g) of each matrix (Q, K, V by whole heads; gate and up by t
 the full activation; after each launch the [B, n/g] slice that the next launch consumes is
 all-gathered over NVLink, so that every rank again holds the full [B, n] activation (four gathers per
 block: Q, o_proj, gate/up, down; the K and V slices stay on their rank, as their consumer --
-attention -- is head-parallel).
+attention -- is head-parallel).  Two gather implementations: `comm="nccl"` calls NCCL's all-gather after
+each launch; `comm="p2p"` fuses the gather into the decode kernel -- every output element is stored
+straight into all ranks' peer-mapped activation buffers, and the kernel itself waits for its peers before
+it reads its activations and publishes its completion to them, so a block is four launches and nothing
+else; `comm="p2p_barrier"` keeps the stores but separates the hand-shake into a one-CTA barrier kernel
+after each launch.
 
 Only the linears and the gathers are in the step: attention, normalisation and residual adds of a
 real model are other kernels and are outside this path.  Each block reads the step's hidden state
@@ -86,6 +91,7 @@ def _rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
 @dataclass
 class _Block:
     bits: int
+    qkv: PackedLinearWeight
     q: PackedLinearWeight
     k: PackedLinearWeight
     v: PackedLinearWeight
@@ -99,7 +105,8 @@ class DecodeStack:
     """The packed linears of `n_blocks` transformer blocks on one rank of a `world`-way column split."""
 
     def __init__(self, n_blocks: int = 32, d_model: int = 4096, d_ff: int = 11008, bitmap: Optional[List[int]] = None,
-                 rank: int = 0, world: int = 1, device="cuda", seed: int = 0, std: float = 0.02, group_size: int = 128):
+                 rank: int = 0, world: int = 1, device="cuda", seed: int = 0, std: float = 0.02, group_size: int = 128,
+                 comm: str = "nccl"):
         if d_model % world or d_ff % world or (d_model // world) % 2:
             raise ValueError("d_model and d_ff must divide evenly over the ranks")
         self.n_blocks, self.d_model, self.d_ff = n_blocks, d_model, d_ff
@@ -107,6 +114,9 @@ class DecodeStack:
         self.bitmap = list(bitmap) if bitmap is not None else sample_bitmap(n_blocks, seed)
         if len(self.bitmap) != n_blocks:
             raise ValueError("bitmap length does not match the number of blocks")
+        if comm not in ("nccl", "p2p", "p2p_barrier"):
+            raise ValueError(comm)
+        self.comm = comm if world > 1 else "nccl"
         self.blocks: List[_Block] = []
         self.workspace = new_workspace(self.device)
         gen = torch.Generator(device=self.device)
@@ -116,11 +126,16 @@ class DecodeStack:
             return torch.randn(n, k, generator=gen, device=self.device, dtype=torch.float32) * std
 
         for i, bits in enumerate(self.bitmap):
+            # this rank's Q, K, V heads live in one row-concatenated matrix; q / k / v are row slices of it
+            qkv = quantize_pack(torch.cat([_rows(draw(i, j, d_model, d_model), rank, world) for j in (1, 2, 3)]), bits, group_size)
+            dl = d_model // world
+
+            def part(j, w=qkv, dl=dl):
+                return PackedLinearWeight(w.packed[j * dl:(j + 1) * dl], w.scales[j * dl:(j + 1) * dl],
+                                          w.zeros[j * dl:(j + 1) * dl], w.bits, w.group_size, w.in_features, dl)
+
             blk = _Block(
-                bits=bits,
-                q=quantize_pack(_rows(draw(i, 1, d_model, d_model), rank, world), bits, group_size),
-                k=quantize_pack(_rows(draw(i, 2, d_model, d_model), rank, world), bits, group_size),
-                v=quantize_pack(_rows(draw(i, 3, d_model, d_model), rank, world), bits, group_size),
+                bits=bits, qkv=qkv, q=part(0), k=part(1), v=part(2),
                 o=quantize_pack(_rows(draw(i, 4, d_model, d_model), rank, world), bits, group_size),
                 gate=quantize_pack(_rows(draw(i, 5, d_ff, d_model), rank, world), bits, group_size),
                 up=quantize_pack(_rows(draw(i, 6, d_ff, d_model), rank, world), bits, group_size),
@@ -133,7 +148,7 @@ class DecodeStack:
         activations read and written by its launches (weights counted once for any batch <= 8)."""
         total = 0
         for blk in self.blocks:
-            for w in (blk.q, blk.k, blk.v, blk.o, blk.gate, blk.up, blk.down):
+            for w in (blk.qkv, blk.o, blk.gate, blk.up, blk.down):
                 total += w.packed.numel() * 4 + w.scales.numel() * 2 * 2
             total += batch * 2 * (self.d_model + 3 * blk.q.out_features)         # QKV in / out
             total += batch * 2 * (self.d_model + blk.o.out_features)
@@ -142,7 +157,83 @@ class DecodeStack:
         return total
 
     def launches_per_step(self) -> int:
-        return 4 * self.n_blocks
+        return (8 if self.comm == "p2p_barrier" else 4) * self.n_blocks   # own kernels; NCCL's are not counted
+
+    # -------------------------------------------------------------- peer-mapped buffers for comm="p2p"
+    def _setup_p2p(self, max_batch: int = 8):
+        """One symmetric allocation per rank: gathered activations Q, A (o_proj out), Y (down out) [8, d], M
+        (gate/up out) [8, f], then the barrier flags.  Every rank learns every peer's base address."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        d, f, esz = self.d_model, self.d_ff, 2
+        self._off = {"q": 0, "a": max_batch * d * esz, "y": 2 * max_batch * d * esz, "m": 3 * max_batch * d * esz}
+        self._off["flags"] = (3 * max_batch * d * esz + max_batch * f * esz + 255) // 256 * 256
+        total = self._off["flags"] + 256
+        self._symm = symm.empty(total, dtype=torch.uint8, device=self.device)
+        self._symm.zero_()
+        self._hdl = symm.rendezvous(self._symm, dist.group.WORLD)
+        self._peer_base = [int(p) for p in self._hdl.buffer_ptrs]
+        self._epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._pstatus = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._done = torch.zeros(1, dtype=torch.int32, device=self.device)
+        from . import _C
+        flags = [b + self._off["flags"] for b in self._peer_base]
+        self._sync = _C.PeerSync(flags, self._symm[self._off["flags"]:self._off["flags"] + 256], self._epoch,
+                                 self._done, self._pstatus, self.rank) if self.comm == "p2p" else None
+        self._local = {k: self._symm[o:] for k, o in self._off.items()}
+        self._qkv_local = None
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    def _buf(self, name: str, batch: int, width: int) -> torch.Tensor:
+        return self._local[name][: batch * width * 2].view(torch.float16).view(batch, width)
+
+    def _barrier(self):
+        if self._sync is not None:
+            return          # the decode kernels carry the hand-shake
+        from . import _C
+        _C.peer_barrier([b + self._off["flags"] for b in self._peer_base], self._local["flags"][:256], self._epoch,
+                        self._pstatus, self.rank)
+
+    def _step_p2p(self, x: torch.Tensor) -> torch.Tensor:
+        from . import _C
+        from .ops import _resolve
+        if not hasattr(self, "_symm"):
+            self._setup_p2p()
+        B, d, f, g, r = x.shape[0], self.d_model, self.d_ff, self.world, self.rank
+        dl, fl = d // g, f // g
+        peers = lambda name: [b + self._off[name] for b in self._peer_base]
+        if self._qkv_local is None or self._qkv_local.shape[0] != B:
+            self._qkv_local = torch.empty(B, 3 * dl, dtype=torch.float16, device=self.device)
+            self._o_local = torch.empty(B, dl, dtype=torch.float16, device=self.device)
+            self._m_local = torch.empty(B, fl, dtype=torch.float16, device=self.device)
+        none = torch.empty(0, dtype=torch.float16, device=self.device)
+        sk = lambda rows, k: _resolve(None, 1, B, rows, k, self.device)
+        xq, xa, xm, xy = self._buf("q", B, d), self._buf("a", B, d), self._buf("m", B, f), self._buf("y", B, d)
+        for blk in self.blocks:
+            w = blk.qkv
+            _C.packed_gemv_scatter(x, w.packed, w.scales, w.zeros, none, self._qkv_local, peers("q"), dl, d, r * dl,
+                                   w.bits, d, w.group_size, sk(3 * dl, d), 1, 0, self._sync)
+            self._barrier()
+            w = blk.o
+            _C.packed_gemv_scatter(xq, w.packed, w.scales, w.zeros, none, self._o_local, peers("a"), dl, d, r * dl,
+                                   w.bits, d, w.group_size, sk(dl, d), 1, 0, self._sync)
+            self._barrier()
+            wg, wu = blk.gate, blk.up
+            _C.fused_gate_up_scatter(xa, wg.packed, wg.scales, wg.zeros, wu.packed, wu.scales, wu.zeros, self._m_local,
+                                     peers("m"), fl, f, r * fl, wg.bits, d, wg.group_size, sk(2 * fl, d), 1, self._sync)
+            self._barrier()
+            w = blk.down
+            _C.packed_gemv_scatter(xm, w.packed, w.scales, w.zeros, none, self._o_local, peers("y"), dl, d, r * dl,
+                                   w.bits, f, w.group_size, sk(dl, f), 1, 0, self._sync)
+            self._barrier()
+        if self._sync is not None:
+            _C.peer_wait(self._sync)     # the peers' last slices have landed before anyone reads the result
+        return xy
+
+    def peer_status(self) -> int:
+        """0 when every barrier heard from every peer in time (after a synchronize)."""
+        return int(self._pstatus.item()) if hasattr(self, "_pstatus") else 0
 
     # -------------------------------------------------------------- one decode step
     def gather(self, t: torch.Tensor) -> torch.Tensor:
@@ -160,6 +251,8 @@ class DecodeStack:
 
     def step(self, x: torch.Tensor, decode_threshold: int = 8) -> torch.Tensor:
         """x [B, d_model] (replicated on every rank) -> the last block's down-projection output [B, d_model]."""
+        if self.comm != "nccl":
+            return self._step_p2p(x)
         y = None
         kw = dict(decode_threshold=decode_threshold, workspace=self.workspace)
         for blk in self.blocks:

@@ -39,13 +39,15 @@ int sm_count_current() {
 int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, int64_t rho, bool pdl,
                        void* scratch, size_t scratch_bytes, cudaStream_t stream);
 int stream_status_read_and_clear(int* out);
+int launch_peer_wait(const GemvParams& P, cudaStream_t stream);
+int launch_peer_signal(const GemvParams& P, cudaStream_t stream);
 int gemm_status_read_and_clear(int* out);
 int launch_gemm_tc(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
                    int64_t gs, int act, cudaStream_t stream);
 
 // Programmatic dependent launch for the streamlined decode kernel (on unless CRISPYBITS_PDL=0).
 static int g_pdl = -1;
-static bool pdl_enabled() {
+bool pdl_enabled() {
     if (g_pdl < 0) {
         const char* e = getenv("CRISPYBITS_PDL");
         g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
@@ -145,11 +147,19 @@ int run_decode(const char* who, const void* x, GemvParams& P, int bits, int64_t 
         const int rc = launch_gemv_stream(bits, dtype, x, P, rho, pdl_enabled(), scratch, scratch_bytes, stream);
         if (rc != -1) return rc;
     }
+    // The generic kernels do not carry the rank hand-shake: bracket them with its two halves.
+    const bool sync = P.sync.on != 0;
+    GemvParams G = P;
+    G.sync.on = 0;
+    int rc = sync ? launch_peer_wait(P, stream) : CB_OK;
+    if (rc != CB_OK) return rc;
     switch (bits) {
-        case 2: return launch_gemv_generic_w2(dtype, x, P, rho, stream);
-        case 3: return launch_gemv_generic_w3(dtype, x, P, rho, stream);
-        default: return launch_gemv_generic_w4(dtype, x, P, rho, stream);
+        case 2: rc = launch_gemv_generic_w2(dtype, x, G, rho, stream); break;
+        case 3: rc = launch_gemv_generic_w3(dtype, x, G, rho, stream); break;
+        default: rc = launch_gemv_generic_w4(dtype, x, G, rho, stream); break;
     }
+    if (rc != CB_OK) return rc;
+    return sync ? launch_peer_signal(P, stream) : CB_OK;
 }
 
 }  // namespace
@@ -211,6 +221,75 @@ int cb_packed_gemv(const void* x, int64_t B, const cb_weight* w, void* out, int6
     P.p[1] = P.p[0]; P.p[2] = P.p[0];
     P.V = (int)w->n; P.B = (int)B; P.K = (int)K; P.act = act;
     return run_decode("packed_gemv", x, P, bits, group_size, dtype, split_k, rho, scratch, scratch_bytes,
+                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+static int fill_scatter(const char* who, GemvParams& P, const cb_scatter* sc, int64_t rows) {
+    if (sc == nullptr) return CB_OK;
+    CB_REQUIRE(sc->world >= 1 && sc->world <= 8, "%s: scatter world must be 1..8", who);
+    CB_REQUIRE(sc->n_gather >= 0 && sc->n_gather <= rows, "%s: n_gather out of range", who);
+    CB_REQUIRE(sc->ld > 0 && sc->col >= 0 && sc->col + sc->n_gather <= sc->ld, "%s: scatter columns out of range", who);
+    for (int i = 0; i < sc->world; ++i) {
+        CB_REQUIRE(sc->peer_out[i] != nullptr, "%s: scatter target %d is NULL", who, i);
+        P.peer_out[i] = sc->peer_out[i];
+    }
+    P.n_peers = sc->world; P.n_gather = (int)sc->n_gather; P.peer_ld = (int)sc->ld; P.peer_col = (int)sc->col;
+    if (sc->sync) {
+        CB_REQUIRE(sc->my_flags && sc->epoch && sc->done && sc->status && sc->rank >= 0 && sc->rank < sc->world,
+                   "%s: scatter hand-shake needs my_flags, epoch, done, status and a rank below world", who);
+        for (int i = 0; i < sc->world; ++i) {
+            CB_REQUIRE(sc->peer_flags[i] != nullptr, "%s: peer %d has no flag array", who, i);
+            P.sync.peer_flags[i] = reinterpret_cast<unsigned int*>(sc->peer_flags[i]);
+        }
+        P.sync.my_flags = reinterpret_cast<unsigned int*>(sc->my_flags);
+        P.sync.epoch = reinterpret_cast<unsigned int*>(sc->epoch);
+        P.sync.done = reinterpret_cast<int*>(sc->done);
+        P.sync.status = sc->status;
+        P.sync.rank = sc->rank;
+        P.sync.on = 1;
+    }
+    return CB_OK;
+}
+
+int cb_packed_gemv_scatter(const void* x, int64_t B, const cb_weight* w, void* out, const cb_scatter* scatter,
+                           int64_t K, int bits, int64_t group_size, int dtype, int64_t split_k, int64_t rho, int act,
+                           void* scratch, size_t scratch_bytes, void* stream) {
+    int rc = check_common("packed_gemv_scatter", x, B, K, bits, group_size, dtype);
+    if (rc) return rc;
+    if ((rc = check_weight("packed_gemv_scatter", w, bits))) return rc;
+    CB_REQUIRE(act >= 0 && act <= 2, "packed_gemv_scatter: act must be 0 (none), 1 (relu) or 2 (silu)");
+    CB_REQUIRE(split_k >= 1, "packed_gemv_scatter: split_k must be >= 1");
+    if (B == 0) return CB_OK;
+    CB_REQUIRE(out != nullptr, "packed_gemv_scatter: out is NULL");
+    GemvParams P{};
+    P.mode = CB_MODE_GEMV;
+    P.p[0] = make_proj(w, out);
+    P.p[1] = P.p[0]; P.p[2] = P.p[0];
+    P.V = (int)w->n; P.B = (int)B; P.K = (int)K; P.act = act;
+    if ((rc = fill_scatter("packed_gemv_scatter", P, scatter, w->n))) return rc;
+    return run_decode("packed_gemv_scatter", x, P, bits, group_size, dtype, split_k, rho, scratch, scratch_bytes,
+                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cb_fused_gate_up_scatter(const void* x, int64_t B, const cb_weight* gate, const cb_weight* up, void* out,
+                             const cb_scatter* scatter, int64_t K, int bits, int64_t group_size, int dtype,
+                             int64_t split_k, int64_t rho, void* scratch, size_t scratch_bytes, void* stream) {
+    int rc = check_common("fused_gate_up_scatter", x, B, K, bits, group_size, dtype);
+    if (rc) return rc;
+    if ((rc = check_weight("fused_gate_up_scatter(gate)", gate, bits))) return rc;
+    if ((rc = check_weight("fused_gate_up_scatter(up)", up, bits))) return rc;
+    CB_REQUIRE(gate->n == up->n, "fused_gate_up_scatter: gate/up shapes must match");
+    CB_REQUIRE(split_k >= 1, "fused_gate_up_scatter: split_k must be >= 1");
+    if (B == 0) return CB_OK;
+    CB_REQUIRE(out != nullptr, "fused_gate_up_scatter: out is NULL");
+    GemvParams P{};
+    P.mode = CB_MODE_GATEUP;
+    P.p[0] = make_proj(gate, out); P.p[0].b = nullptr;
+    P.p[1] = make_proj(up, out);   P.p[1].b = nullptr;
+    P.p[2] = P.p[0];
+    P.V = 2 * (int)gate->n; P.B = (int)B; P.K = (int)K; P.act = 0;
+    if ((rc = fill_scatter("fused_gate_up_scatter", P, scatter, gate->n))) return rc;
+    return run_decode("fused_gate_up_scatter", x, P, bits, group_size, dtype, split_k, rho, scratch, scratch_bytes,
                       reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -43,6 +43,18 @@ struct Proj {
     int n;
 };
 
+// Rank-to-rank hand-shake of a column-parallel stack, carried by the decode kernel itself: before it reads
+// its activations a launch waits until every peer has completed as many launches as this rank, and its last
+// CTA to finish tells every peer that one more launch is complete.
+struct PeerSync {
+    unsigned int* peer_flags[8];  // peer_flags[p] = rank p's flag array (one uint32 per rank), peer-mapped
+    unsigned int* my_flags;       // this rank's own flag array: my_flags[p] = launches rank p has completed
+    unsigned int* epoch;          // launches this rank has completed
+    int* done;                    // CTAs of the running launch that are finished; zero between launches
+    int* status;                  // 0, or 1 + the first peer that was not heard from in time
+    int rank, on;
+};
+
 struct GemvParams {
     Proj p[3];
     int mode;                 // CB_MODE_*
@@ -55,7 +67,59 @@ struct GemvParams {
     const float* rope_cos;    // [B, head_dim] fp32 or nullptr
     const float* rope_sin;
     int head_dim, perm_hd;
+    // Optional peer scatter (column-parallel stacks): output rows r < n_gather of GEMV / gate-up mode are
+    // stored into every rank's gathered activation buffer at [b * peer_ld + peer_col + r] instead of `out`.
+    void* peer_out[8];
+    int n_peers, n_gather, peer_ld, peer_col;
+    PeerSync sync;
 };
+
+constexpr long long kPeerWaitCycles = 2000000000ll;   // about a second
+
+// All threads of the CTA call this before the first read of the activations.  Threads 0..world-1 each watch one
+// peer's counter; the wait is bounded, and once one wait has run out (status != 0) later ones return at once.
+// Returns (to thread 0) the number of launches this rank had completed, which peer_signal advances.
+__device__ __forceinline__ unsigned int peer_wait(const GemvParams& P) {
+    if (!P.sync.on) return 0u;
+    const int p = threadIdx.x;
+    unsigned int e = 0u;
+    if (p < P.n_peers) {
+        e = *reinterpret_cast<volatile unsigned int*>(P.sync.epoch);
+        unsigned int seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(P.sync.my_flags + p) : "memory");
+        if ((int)(seen - e) < 0 && *reinterpret_cast<volatile int*>(P.sync.status) == 0) {
+            const long long t0 = clock64();
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(P.sync.my_flags + p) : "memory");
+                if ((int)(seen - e) >= 0) break;
+                if (clock64() - t0 > kPeerWaitCycles) { atomicCAS(P.sync.status, 0, 1 + p); break; }
+                __nanosleep(64);
+            }
+        }
+    }
+    __syncthreads();
+    return e;
+}
+
+// All threads of every CTA call this once, after their last store; `e` is what peer_wait returned.  The CTA
+// barrier puts every thread's stores before thread 0's system-scope fence, the arrival counter chains the CTAs,
+// and the last CTA to arrive fences again before it advances this rank's launch count and publishes it: all
+// output stores of the grid (peer stores included) are visible to a peer that sees the new count.
+__device__ __forceinline__ void peer_signal(const GemvParams& P, unsigned int e) {
+    if (!P.sync.on) return;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        if (atomicAdd(P.sync.done, 1) == (int)gridDim.x - 1) {
+            *P.sync.done = 0;
+            const unsigned int e1 = e + 1u;
+            *reinterpret_cast<volatile unsigned int*>(P.sync.epoch) = e1;
+            __threadfence_system();
+            for (int q = 0; q < P.n_peers; ++q)
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(P.sync.peer_flags[q] + P.sync.rank), "r"(e1) : "memory");
+        }
+    }
+}
 
 // Virtual row -> (projection, row inside it).  GEMV: identity; QKV: three consecutive ranges;
 // gate/up: even virtual rows are gate rows, odd ones the up row of the same index, so that the two
@@ -90,13 +154,22 @@ template <typename T>
 __device__ __forceinline__ void epilogue(const GemvParams& P, int b, int v, float mine, float partner) {
     int proj, r;
     map_row(P, v, proj, r);
-    if (P.mode == CB_MODE_GEMV) {
-        const float y = activate(mine + bias_at<T>(P.p[0].b, r), P.act);
-        reinterpret_cast<T*>(P.p[0].out)[(size_t)b * P.p[0].n + r] = from_f32<T>(y);
-    } else if (P.mode == CB_MODE_GATEUP) {
-        if (proj != 0) return;  // the gate row writes silu(gate) * up
-        const float y = activate(mine, CB_ACT_SILU) * partner;
-        reinterpret_cast<T*>(P.p[0].out)[(size_t)b * P.p[0].n + r] = from_f32<T>(y);
+    if (P.mode == CB_MODE_GEMV || P.mode == CB_MODE_GATEUP) {
+        float y;
+        if (P.mode == CB_MODE_GEMV) {
+            y = activate(mine + bias_at<T>(P.p[0].b, r), P.act);
+        } else {
+            if (proj != 0) return;  // the gate row writes silu(gate) * up
+            y = activate(mine, CB_ACT_SILU) * partner;
+        }
+        const T yt = from_f32<T>(y);
+        if (r < P.n_gather) {
+            // the all-gather is these stores: the slice goes straight into every rank's buffer over NVLink
+            const size_t at = (size_t)b * P.peer_ld + P.peer_col + r;
+            for (int q = 0; q < P.n_peers; ++q) reinterpret_cast<T*>(P.peer_out[q])[at] = yt;
+        } else {
+            reinterpret_cast<T*>(P.p[0].out)[(size_t)b * P.p[0].n + r] = yt;
+        }
     } else {
         const Proj& pr = P.p[proj];
         float y = mine + bias_at<T>(pr.b, r);
@@ -116,6 +189,7 @@ __device__ __forceinline__ void epilogue(const GemvParams& P, int b, int v, floa
 // ---- host side ------------------------------------------------------------------------------
 void set_error(const char* fmt, ...);
 int sm_count_current();
+bool pdl_enabled();   // programmatic dependent launches are in use (on unless switched off)
 
 #define CB_CUDA_TRY(expr)                                                                  \
     do {                                                                                   \

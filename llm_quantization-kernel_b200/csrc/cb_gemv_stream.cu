@@ -301,6 +301,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
 
     // Wait until everything the previous kernel wrote (our activations, the scratch) is visible.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const unsigned int peer_epoch = peer_wait(P);      // sharded stacks: the peers' slices of our activations have landed
     CB_STAMP(2);
 
     const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -457,6 +458,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
             if (tid == 0) P.counters[slab] = 0;
         }
     }
+    peer_signal(P, peer_epoch);
 }
 
 template <int BITS>
