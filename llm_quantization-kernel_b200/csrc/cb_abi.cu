@@ -38,6 +38,7 @@ int sm_count_current() {
 
 int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, int64_t rho, bool pdl,
                        void* scratch, size_t scratch_bytes, cudaStream_t stream);
+int launch_gemv_direct(int bits, int dtype, const void* x, const GemvParams& P, bool pdl, cudaStream_t stream);
 int stream_status_read_and_clear(int* out);
 int launch_peer_wait(const GemvParams& P, cudaStream_t stream);
 int launch_peer_signal(const GemvParams& P, cudaStream_t stream);
@@ -55,6 +56,8 @@ bool pdl_enabled() {
     return g_pdl != 0;
 }
 static int g_force_generic = 0;
+static int g_no_direct = 0;
+static int g_prefer_direct = -1;   // -1: by shape, 1: wherever it applies
 
 int launch_unpack(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, cudaStream_t stream);
 int launch_gemm_simt(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
@@ -142,8 +145,18 @@ int run_decode(const char* who, const void* x, GemvParams& P, int bits, int64_t 
         P.counters = reinterpret_cast<int*>(scratch);
         P.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kCounterBytes);
     }
+    // Measured on B200: with one or two batch rows the register-streaming kernel is the faster one once every
+    // CTA has several 16-row tiles to stream through; the ring kernel wins on matrices of few rows, where its
+    // single pass overlaps the neighbouring launches, and for larger batches, where every CTA of the register
+    // kernel would stage all B activation rows.
+    const bool direct_first = g_prefer_direct == 1 || (g_prefer_direct < 0 && P.B <= 2 && P.V >= 8192);
+    if (!g_force_generic && !g_no_direct && direct_first) {
+        // the register-streaming fp16 kernel when the problem is inside its domain (-1 = it is not)
+        const int rc = launch_gemv_direct(bits, dtype, x, P, pdl_enabled(), stream);
+        if (rc != -1) return rc;
+    }
     if (!g_force_generic) {
-        // the streamlined fp16 kernel when the problem is inside its domain (-1 = it is not)
+        // then the shared-memory ring kernel
         const int rc = launch_gemv_stream(bits, dtype, x, P, rho, pdl_enabled(), scratch, scratch_bytes, stream);
         if (rc != -1) return rc;
     }
@@ -182,6 +195,7 @@ int cb_sm_count(void) { return sm_count_current(); }
 void cb_set_option(int option, int value) {
     if (option == 0) g_pdl = value ? 1 : 0;
     if (option == 1) g_force_generic = value ? 1 : 0;
+    if (option == 2) { g_no_direct = value == 1 ? 1 : 0; g_prefer_direct = value == 2 ? 1 : -1; }
 }
 
 int cb_decode_status(int* status) {

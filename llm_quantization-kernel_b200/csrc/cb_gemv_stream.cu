@@ -26,16 +26,18 @@
 #include <algorithm>
 
 #include "cb_common.cuh"
+#include "cb_frag.cuh"
 
 namespace cb {
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
-constexpr int kRowsPerPass = 32;          // two 16-row MMA tiles
-constexpr int kMaxBuf = 3;
+constexpr int kMaxRowsPerPass = 32;       // a pass is one or two 16-row MMA tiles (StreamParams::rpp)
+constexpr int kMaxBuf = 6;
 constexpr int kSpinLimit = 1 << 22;       // bounded mbarrier wait (~ a second), then give up and flag
-constexpr size_t kSmemCap = 220 * 1024;
+constexpr size_t kSmemCap = 220 * 1024;       // one CTA per SM
+constexpr size_t kSmemCapTwo = 112 * 1024;    // two CTAs per SM
 
 __device__ int g_stream_status;
 #ifdef CB_STREAM_TIMING
@@ -53,13 +55,21 @@ __device__ __forceinline__ unsigned long long now_ns() {
 #define CB_STAMP(i) do { } while (0)
 #endif           // 0 = ok; else the pass whose copy never landed, plus one
 
+#ifdef CB_STREAM_DEBUG
+#define CB_DBG(bit) (S.dbg & (bit))
+#else
+#define CB_DBG(bit) 0
+#endif
+
 struct StreamParams {
     GemvParams g;
     int nslabs;            // CTAs per K-partition
     int nbuf;              // ring depth
+    int rpp;               // rows per pass: 32 or 16
+    int dbg;               // diagnostic builds only: parts of the kernel to leave out
     int pitch;             // shared-memory bytes per staged row (row bytes + bank-spreading pad)
     int meta_stride;       // shared-memory bytes per staged row of scales (and of zeros)
-    int slot_bytes;        // one ring slot: 32 weight rows, 32 scale rows, 32 zero rows
+    int slot_bytes;        // one ring slot: rpp weight rows, rpp scale rows, rpp zero rows
     int xb_stride;         // shared-memory bytes between batch rows of the staged activations
     int pair_q, pair_r;    // row pairs per slab: quotient and remainder of (V/2) / nslabs
     int grp_q, grp_r;      // group PAIRS per K-partition: quotient and remainder of (groups/2) / split_k
@@ -95,122 +105,6 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));
-    return r;
-}
-__device__ __forceinline__ uint32_t h2fma(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t r;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
-__device__ __forceinline__ uint32_t h2add(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t a0, const uint32_t a1, const uint32_t a2,
-                                         const uint32_t a3, const uint32_t b0, const uint32_t b1, const float (&c)[4]) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
-}
-
-constexpr uint32_t kMagic = 0x64006400u;      // half2(1024, 1024)
-
-__device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-
-// The 32 codes of one chunk -> 16 half2 registers holding the exact integers (code - zero).  e[m] holds
-// the code pair (pair_lo(m), pair_lo(m) + pair_gap()) in its (low, high) half.  A field that sits at
-// bit p of a half is extracted in place: (w & mask) | 0x6400 reads as 1024 + code * 2^p, and one
-// fused multiply-add with 2^-p and the constant -(1024 * 2^-p + zero) leaves code - zero, exactly.
-// `consts()` prepares those constants for one (row, group) from the group's zero point.
-template <int BITS> struct Unpack;
-
-template <> struct Unpack<4> {
-    static constexpr int kConsts = 2;
-    __device__ static __forceinline__ int pair_lo(int m) { return 8 * (m >> 2) + (m & 3); }   // word i: e[4i+j] = (8i+j, 8i+j+4)
-    __device__ static __forceinline__ int pair_gap() { return 4; }
-    __device__ static __forceinline__ void consts(uint32_t zz, uint32_t (&k)[kConsts]) {
-        k[0] = h2sub(0xE400E400u, zz);     // -(1024 + z)
-        k[1] = h2sub(0xD400D400u, zz);     // -(64 + z)
-    }
-    __device__ static __forceinline__ void run(const uint32_t (&w)[4], const uint32_t (&k)[kConsts], uint32_t (&e)[16]) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t lo = w[i], hi = w[i] >> 8;
-            e[4 * i + 0] = h2add(lop3_and_or(lo, 0x000F000Fu, kMagic), k[0]);
-            e[4 * i + 1] = h2fma(lop3_and_or(lo, 0x00F000F0u, kMagic), 0x2C002C00u, k[1]);   // * 1/16
-            e[4 * i + 2] = h2add(lop3_and_or(hi, 0x000F000Fu, kMagic), k[0]);
-            e[4 * i + 3] = h2fma(lop3_and_or(hi, 0x00F000F0u, kMagic), 0x2C002C00u, k[1]);
-        }
-    }
-};
-
-template <> struct Unpack<2> {
-    static constexpr int kConsts = 5;
-    __device__ static __forceinline__ int pair_lo(int m) { return 16 * (m >> 3) + (m & 7); }  // word i: e[8i+j] = (16i+j, 16i+j+8)
-    __device__ static __forceinline__ int pair_gap() { return 8; }
-    __device__ static __forceinline__ void consts(uint32_t zz, uint32_t (&k)[kConsts]) {
-        k[0] = h2sub(0xE400E400u, zz);     // -(1024 + z)
-        k[1] = h2sub(0xDC00DC00u, zz);     // -(256 + z)
-        k[2] = h2sub(0xD400D400u, zz);     // -(64 + z)
-        k[3] = h2sub(0xCC00CC00u, zz);     // -(16 + z)
-        k[4] = h2sub(0xC400C400u, zz);     // -(4 + z)
-    }
-    __device__ static __forceinline__ void run(const uint32_t (&w)[2], const uint32_t (&k)[kConsts], uint32_t (&e)[16]) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const uint32_t lo = w[i], hi = w[i] >> 10;
-            e[8 * i + 0] = h2add(lop3_and_or(lo, 0x00030003u, kMagic), k[0]);
-            e[8 * i + 1] = h2fma(lop3_and_or(lo, 0x000C000Cu, kMagic), 0x34003400u, k[1]);   // * 1/4
-            e[8 * i + 2] = h2fma(lop3_and_or(lo, 0x00300030u, kMagic), 0x2C002C00u, k[2]);   // * 1/16
-            e[8 * i + 3] = h2fma(lop3_and_or(lo, 0x00C000C0u, kMagic), 0x24002400u, k[3]);   // * 1/64
-            e[8 * i + 4] = h2fma(lop3_and_or(lo, 0x03000300u, kMagic), 0x1C001C00u, k[4]);   // * 1/256
-            e[8 * i + 5] = h2add(lop3_and_or(hi, 0x00030003u, kMagic), k[0]);
-            e[8 * i + 6] = h2fma(lop3_and_or(hi, 0x000C000Cu, kMagic), 0x34003400u, k[1]);
-            e[8 * i + 7] = h2fma(lop3_and_or(hi, 0x00300030u, kMagic), 0x2C002C00u, k[2]);
-        }
-    }
-};
-
-template <> struct Unpack<3> {
-    // e[j] = (code j, code j+16): the chunk is a 96-bit stream; code j sits at bit 3j, code j+16 at bit
-    // 3j+48.  Windows of 15 bits (5 codes) of both halves are brought side by side into one register
-    // with funnel shifts (which also reassemble the codes that straddle a word) and a byte permute.
-    static constexpr int kConsts = 3;
-    __device__ static __forceinline__ int pair_lo(int m) { return m; }
-    __device__ static __forceinline__ int pair_gap() { return 16; }
-    __device__ static __forceinline__ void consts(uint32_t zz, uint32_t (&k)[kConsts]) {
-        k[0] = h2sub(0xE400E400u, zz);     // -(1024 + z)
-        k[1] = h2sub(0xD800D800u, zz);     // -(128 + z)
-        k[2] = h2sub(0xCC00CC00u, zz);     // -(16 + z)
-    }
-    __device__ static __forceinline__ void five(uint32_t p, const uint32_t (&k)[kConsts], uint32_t* e) {
-        const uint32_t q = p >> 9;
-        e[0] = h2add(lop3_and_or(p, 0x00070007u, kMagic), k[0]);
-        e[1] = h2fma(lop3_and_or(p, 0x00380038u, kMagic), 0x30003000u, k[1]);   // * 1/8
-        e[2] = h2fma(lop3_and_or(p, 0x01C001C0u, kMagic), 0x24002400u, k[2]);   // * 1/64
-        e[3] = h2add(lop3_and_or(q, 0x00070007u, kMagic), k[0]);
-        e[4] = h2fma(lop3_and_or(q, 0x00380038u, kMagic), 0x30003000u, k[1]);
-    }
-    __device__ static __forceinline__ void run(const uint32_t (&w)[3], const uint32_t (&k)[kConsts], uint32_t (&e)[16]) {
-        // stream bits [s, s+16) of the first half next to bits [48+s, 48+s+16) of the second half
-        const uint32_t l1 = __funnelshift_r(w[0], w[1], 15), l2 = __funnelshift_r(w[0], w[1], 30);
-        const uint32_t u0 = __funnelshift_r(w[1], w[2], 16), u1 = __funnelshift_r(w[1], w[2], 31), u2 = w[2] >> 14;
-        five(__byte_perm(w[0], u0, 0x5410), k, e);
-        five(__byte_perm(l1, u1, 0x5410), k, e + 5);
-        five(__byte_perm(l2, u2, 0x5410), k, e + 10);
-        const uint32_t last = __byte_perm(w[1] >> 13, w[2] >> 29, 0x5410);               // codes 15 and 31
-        e[15] = h2add(lop3_and_or(last, 0x00070007u, kMagic), k[0]);
-    }
-};
-
 // One chunk (BITS words) from shared memory with the widest load its alignment allows.
 template <int BITS> __device__ __forceinline__ void lds_chunk(const unsigned char* p, uint32_t (&w)[BITS]) {
     if constexpr (BITS == 4) {
@@ -224,10 +118,6 @@ template <int BITS> __device__ __forceinline__ void lds_chunk(const unsigned cha
         w[0] = q[0]; w[1] = q[1]; w[2] = q[2];
     }
 }
-
-// Even split of n items into `parts`: part i starts at i*q + min(i, r) with q = n / parts, r = n % parts
-// (q and r come from the host, so the kernel does no division on its way to the first copy).
-__device__ __forceinline__ int split_begin(int i, int q, int r) { return i * q + min(i, r); }
 
 template <int BITS>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -250,7 +140,8 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
     const int ng = 2 * split_begin(split + 1, S.grp_q, S.grp_r) - g_begin;
     const int row_begin = 2 * split_begin(slab, S.pair_q, S.pair_r);
     const int row_end = min(P.V, 2 * split_begin(slab + 1, S.pair_q, S.pair_r));
-    const int npass = (row_end - row_begin + kRowsPerPass - 1) / kRowsPerPass;
+    const int rpp = S.rpp;
+    const int npass = (row_end - row_begin + rpp - 1) / rpp;
     const uint32_t row_bytes = (uint32_t)ng * kGroupBytes;
 
     const uint32_t s_base = smem_u32(smem);
@@ -268,23 +159,23 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
     // after the expect-tx arrival, the bulk bytes, and one arrival per lane once its cp.async landed.
     auto issue_pass = [&](int p) {
         const int buf = p % S.nbuf;
-        const int row0 = row_begin + p * kRowsPerPass;
-        const int nrows = min(kRowsPerPass, row_end - row0);
+        const int row0 = row_begin + p * rpp;
+        const int nrows = min(rpp, row_end - row0);
         const uint32_t slot = s_ring + (uint32_t)buf * S.slot_bytes;
         const uint32_t bar = s_bar + 8 * buf;
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)nrows * row_bytes);
+        if (lane == 0) mbar_expect_tx(bar, CB_DBG(4) ? 0u : (uint32_t)nrows * row_bytes);
         __syncwarp();
         if (lane < nrows) {
             int proj, lr;
             map_row(P, row0 + lane, proj, lr);
             const unsigned char* src = reinterpret_cast<const unsigned char*>(P.p[proj].w) +
                                        ((size_t)lr * P.wpr * 4 + (size_t)g_begin * kGroupBytes);
-            bulk_g2s(slot + (uint32_t)lane * S.pitch, src, row_bytes, bar);
+            if (!CB_DBG(4)) bulk_g2s(slot + (uint32_t)lane * S.pitch, src, row_bytes, bar);
             const __half* ssrc = reinterpret_cast<const __half*>(P.p[proj].s) + (size_t)lr * P.groups + g_begin;
             const __half* zsrc = reinterpret_cast<const __half*>(P.p[proj].z) + (size_t)lr * P.groups + g_begin;
-            const uint32_t sdst = slot + kRowsPerPass * S.pitch + (uint32_t)lane * S.meta_stride;
-            const uint32_t zdst = sdst + kRowsPerPass * S.meta_stride;
-            for (int j = 0; j < ng; j += 2) {
+            const uint32_t sdst = slot + rpp * S.pitch + (uint32_t)lane * S.meta_stride;
+            const uint32_t zdst = sdst + rpp * S.meta_stride;
+            for (int j = 0; j < (CB_DBG(1) ? 0 : ng); j += 2) {
                 cp_async4(sdst + 2 * j, ssrc + j);
                 cp_async4(zdst + 2 * j, zsrc + j);
             }
@@ -330,9 +221,9 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
 
     for (int p = 0; p < npass; ++p) {
         const int buf = p % S.nbuf;
-        const int row0 = row_begin + p * kRowsPerPass;
+        const int row0 = row_begin + p * rpp;
         const uint32_t parity = (uint32_t)((p / S.nbuf) & 1);
-        const int ntile = (min(kRowsPerPass, row_end - row0) + 15) >> 4;
+        const int ntile = (min(rpp, row_end - row0) + 15) >> 4;
         const unsigned char* rbase = smem + S.off_ring + (size_t)buf * S.slot_bytes;
         float* myred = red + (size_t)(p & 1) * (kWarps * 2 * 32 * 4);
         {   // bounded wait for this pass's rows
@@ -349,7 +240,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-        for (int gl = wg_begin; gl < wg_end; ++gl) {
+        for (int gl = wg_begin; gl < (CB_DBG(2) ? wg_begin : wg_end); ++gl) {
             // activations of this group, re-paired to match the unpack order; the next group's are requested now
             uint32_t xf[16];
 #pragma unroll
@@ -357,14 +248,14 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
                 const int lo = Unpack<BITS>::pair_lo(m), hi = lo + Unpack<BITS>::pair_gap();
                 xf[m] = __byte_perm(xnext[lo >> 1], xnext[hi >> 1], (lo & 1) ? 0x7632 : 0x5410);
             }
-            load_x(gl + 1 < wg_end ? gl + 1 : wg_begin, xnext);      // wraps to the first group for the next pass
+            if (!CB_DBG(8)) load_x(gl + 1 < wg_end ? gl + 1 : wg_begin, xnext);      // wraps to the first group for the next pass
 #pragma unroll
             for (int tile = 0; tile < 2; ++tile) {
                 if (tile < ntile) {
                     const unsigned char* arow = rbase + (size_t)(tile * 16 + g) * S.pitch + (size_t)gl * kGroupBytes + (size_t)t * kChunkBytes;
-                    const __half* s0 = reinterpret_cast<const __half*>(rbase + kRowsPerPass * S.pitch + (size_t)(tile * 16 + g) * S.meta_stride);
+                    const __half* s0 = reinterpret_cast<const __half*>(rbase + rpp * S.pitch + (size_t)(tile * 16 + g) * S.meta_stride);
                     const __half* s1 = s0 + 4 * S.meta_stride;                       // 8 rows further (stride is in bytes, pointer in halves)
-                    const __half* z0 = s0 + (kRowsPerPass / 2) * S.meta_stride;      // the zeros follow the 32 scale rows
+                    const __half* z0 = s0 + (rpp / 2) * S.meta_stride;               // the zeros follow the scale rows
                     const __half* z1 = z0 + 4 * S.meta_stride;
                     // rows past the end of the slab were never copied: give them scale 0 and a finite zero point
                     const bool ok0 = row0 + tile * 16 + g < row_end, ok1 = row0 + tile * 16 + g + 8 < row_end;
@@ -377,11 +268,23 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
                     uint32_t wa[BITS], wb[BITS], ea[16], eb[16];
                     lds_chunk<BITS>(arow, wa);
                     lds_chunk<BITS>(arow + 8 * (size_t)S.pitch, wb);
+                    if (CB_DBG(32)) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) { ea[i] = wa[i % BITS] + ka[0]; eb[i] = wb[i % BITS] + kb[0]; }
+                    } else {
                     Unpack<BITS>::run(wa, ka, ea);
                     Unpack<BITS>::run(wb, kb, eb);
+                    }
                     // Four independent accumulation chains of depth two: on this GPU a dependent mma.sync
                     // issues ~110 cycles after its predecessor, so the eight k-steps must not form one chain.
                     float d0[4], d1[4], d2[4], d3[4];
+                    if (CB_DBG(16)) {
+                        uint32_t h = 0;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) h ^= ea[i] ^ eb[i] ^ xf[i];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { d0[j] = __uint_as_float(h & 0x3fffffff); d1[j] = d2[j] = d3[j] = 0.f; }
+                    } else {
                     mma16816(d0, ea[0], eb[0], ea[1], eb[1], xf[0], xf[1], zero4);
                     mma16816(d1, ea[2], eb[2], ea[3], eb[3], xf[2], xf[3], zero4);
                     mma16816(d2, ea[4], eb[4], ea[5], eb[5], xf[4], xf[5], zero4);
@@ -390,6 +293,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
                     mma16816(d1, ea[10], eb[10], ea[11], eb[11], xf[10], xf[11], d1);
                     mma16816(d2, ea[12], eb[12], ea[13], eb[13], xf[12], xf[13], d2);
                     mma16816(d3, ea[14], eb[14], ea[15], eb[15], xf[14], xf[15], d3);
+                    }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) { d0[j] = (d0[j] + d1[j]) + (d2[j] + d3[j]); d1[j] = 0.f; }
                     // acc += s * sum((q - z) x): rows g (d[0], d[1]) and g+8 (d[2], d[3]), batch columns 2t, 2t+1
@@ -424,7 +328,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
                 mine += myred[((w * 2 + tile) * 32 + fl) * 4 + fe];
                 partner += myred[((w * 2 + tile) * 32 + pl) * 4 + fe];
             }
-            if (v < row_end && b < P.B && !failed) {
+            if (tile < ntile && v < row_end && b < P.B && !failed) {
                 if (P.split_k == 1) epilogue<__half>(P, b, v, mine, partner);
                 else P.partial[((size_t)split * P.B + b) * P.V + v] = mine;
             }
@@ -472,7 +376,7 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
     const int gpairs = P.groups / 2;
     int split = std::max(1, std::min(P.split_k, gpairs));
     const int group_bytes = 16 * BITS;
-    auto layout = [&](int sp, int nbuf, StreamParams& out) -> size_t {
+    auto layout = [&](int sp, int nbuf, int rpp, StreamParams& out) -> size_t {
         const int ng = 2 * ((gpairs + sp - 1) / sp);                  // largest partition
         int meta = ng * 2;
         meta += ((4 - meta) % 128 + 128) % 128;                        // rows 4 bytes apart (mod 128): conflict-free 2-byte reads
@@ -481,18 +385,61 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
         int xb = ng * 256;
         xb += ((64 - xb) % 128 + 128) % 128;                          // batch rows 64 bytes apart (mod 128)
         size_t off = 0;
-        out.off_bar = (unsigned)off; off += 64;                      // 2 mbarriers per ring slot, at most 3 slots
+        out.off_bar = (unsigned)off; off += 64;                      // one mbarrier per ring slot, at most 8 slots
         off = (off + 127) & ~(size_t)127;
         out.off_red = (unsigned)off; off += (size_t)2 * kWarps * 2 * 32 * 4 * sizeof(float);
         out.off_x = 0;
         off = (off + 127) & ~(size_t)127;
-        out.slot_bytes = kRowsPerPass * (pitch + 2 * meta);
+        out.slot_bytes = rpp * (pitch + 2 * meta);
         out.off_ring = (unsigned)off; off += (size_t)nbuf * out.slot_bytes;
-        out.pitch = pitch; out.meta_stride = meta; out.xb_stride = xb; out.nbuf = nbuf;
+        out.pitch = pitch; out.meta_stride = meta; out.xb_stride = xb; out.nbuf = nbuf; out.rpp = rpp;
         return off;
     };
-    while (layout(split, 1, S) > kSmemCap && split < gpairs) ++split;
-    if (layout(split, 1, S) > kSmemCap) return -1;
+    const int vpairs = (P.V + 1) / 2;
+    // Slabs, passes and ring depth of a candidate (CTAs, split, rows per pass) under a shared-memory cap.
+    struct Plan { int split, rpp, nbuf, nslabs, npass; bool ok; };
+    auto plan = [&](int ctas, int sp, int rpp, size_t cap) -> Plan {
+        Plan pl{sp, rpp, 0, 0, 0, false};
+        StreamParams tmp{};
+        if (layout(sp, 1, rpp, tmp) > cap) return pl;
+        int nslabs = std::max(1, std::min(ctas / sp, (vpairs + 7) / 8));          // at least 16 rows per slab when possible
+        nslabs = std::min(nslabs, vpairs);
+        const int rows_per_slab = 2 * ((vpairs + nslabs - 1) / nslabs);
+        pl.nslabs = nslabs;
+        pl.npass = (rows_per_slab + rpp - 1) / rpp;
+        pl.nbuf = std::min(pl.npass, kMaxBuf);
+        while (pl.nbuf > 1 && layout(sp, pl.nbuf, rpp, tmp) > cap) --pl.nbuf;
+        pl.ok = true;
+        return pl;
+    };
+    // (1) One CTA per SM covers its rows in a single 32-row pass: do that, and leave the SM's second CTA slot to
+    //     the next launch of the stream, whose prologue and first copies then overlap this launch's arithmetic.
+    // (2) Otherwise prefer a ring that keeps copies in flight during the arithmetic (two slots or more): two CTAs
+    //     per SM (twice the warps to hide latency) with 32- or 16-row passes, else one CTA per SM likewise.
+    // (3) Otherwise one CTA per SM with a single slot, the K split raised until a slot fits.
+    const int per_sm = rho <= 0 ? 2 : (int)std::min<int64_t>(std::max<int64_t>(rho, 2), 4);
+    Plan pick{};
+    {
+        const Plan c = plan(sms, split, 32, kSmemCap);
+        if (rho > 0 && rho <= 2 && c.ok && c.npass == 1) pick = c;
+    }
+    if (!pick.ok) {
+        const struct { int ctas; size_t cap; } tries[2] = {{per_sm * sms, kSmemCapTwo}, {sms, kSmemCap}};
+        for (int i = 0; i < 2 && !pick.ok; ++i)
+            for (int rpp : {32, 16}) {
+                const Plan c = plan(tries[i].ctas, split, rpp, tries[i].cap);
+                if (c.ok && c.nbuf >= std::min(2, c.npass)) { pick = c; break; }
+            }
+    }
+    if (!pick.ok) {
+        int sp = split;
+        while (!plan(sms, sp, 32, kSmemCap).ok && sp < gpairs) ++sp;
+        pick = plan(sms, sp, 32, kSmemCap);
+        if (!pick.ok) return -1;
+    }
+    split = pick.split;
+    const int nslabs = pick.nslabs;
+    if (split > 1 && nslabs > 65536) return -1;
     // scratch: [65536 counters | split x B x V partial sums]; without enough of it this path is not taken
     constexpr size_t kCounterBytes = 65536 * sizeof(int);
     if (split > 1) {
@@ -501,17 +448,11 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
         P.counters = reinterpret_cast<int*>(scratch);
         P.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kCounterBytes);
     }
-    const int ctas = rho <= 0 ? 2 * sms : (int)std::min<int64_t>(rho, 4) * sms;   // rho 0: no persistence wanted -> small slabs
-    const int vpairs = (P.V + 1) / 2;
-    int nslabs = std::max(1, std::min(ctas / split, (vpairs + 7) / 8));           // at least 16 rows per slab when possible
-    nslabs = std::min(nslabs, vpairs);
-    if (split > 1 && nslabs > 65536) return -1;
-    const int rows_per_slab = 2 * ((vpairs + nslabs - 1) / nslabs);
-    const int npass = (rows_per_slab + kRowsPerPass - 1) / kRowsPerPass;
-    int nbuf = std::min(npass, kMaxBuf);
-    while (nbuf > 1 && layout(split, nbuf, S) > kSmemCap) --nbuf;
-    const size_t smem = layout(split, nbuf, S);
+    const size_t smem = layout(split, pick.nbuf, pick.rpp, S);
     P.split_k = split;
+#ifdef CB_STREAM_DEBUG
+    { const char* e = getenv("CB_GEMV_DEBUG"); S.dbg = e ? atoi(e) : 0; }
+#endif
     S.g = P;
     S.nslabs = nslabs;
     S.pair_q = vpairs / nslabs; S.pair_r = vpairs % nslabs;

@@ -229,15 +229,37 @@ def test_streamlined_kernel_agrees_with_generic_kernel(bits, mode):
         cos, sin = rope_tables(3, 128, DEV)
         return [o for sk in (1, 4) for o in fused_qkv(x, q, k, v, sk, 1, rope=(cos, sin, 128))]
 
-    fast = run()
-    _C.set_option(1, 1)
+    outs = {}
     try:
+        for which in (1, 2):           # option 2: 1 = shared-memory ring kernel, 2 = register-streaming kernel
+            _C.set_option(2, which)
+            outs[which] = run()
+        _C.set_option(2, 0)
+        _C.set_option(1, 1)
         slow = run()
     finally:
         _C.set_option(1, 0)
-    for a, b in zip(fast, slow):
-        assert rel_err(a, b.float()) < 1e-3
+        _C.set_option(2, 0)
+    for which in (1, 2):
+        for a, b in zip(outs[which], slow):
+            assert rel_err(a, b.float()) < 1e-3, which
     assert _C.decode_status() == 0
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("B", [1, 5, 8])
+def test_register_streaming_kernel_full_size(bits, B):
+    """The register-streaming decode kernel forced on (option 2 = 2): ragged last tile, several tiles per CTA,
+    uneven K slices (K = 11008 is 43 group pairs over 8 warps), bias and SiLU."""
+    from crispybits_kernels import _C, packed_linear
+    w, wd, bd = cached(5000, 11008, bits, torch.float16, True, 21, 128, 0.02)
+    x = torch.randn(B, 11008, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(B))
+    _C.set_option(2, 2)
+    try:
+        y = packed_linear(x, w, None, 1, "silu")
+    finally:
+        _C.set_option(2, 0)
+    close(y, ref_linear(x, wd, bd, "silu"), torch.float16)
 
 
 def test_decode_status_word_is_clean_after_the_suite_so_far():
