@@ -187,8 +187,9 @@ size_t cb_gemv_scratch_bytes(int64_t B, int64_t V, int64_t split_k);
  * With it on, a decode call may start fetching PACKED WEIGHTS before the previous kernel of the
  * stream has finished; activations, outputs and scratch are only touched afterwards.  option 1:
  * value 1 forces the shape-generic decode kernel everywhere (for A/B checks).  option 2: which
- * fp16 decode kernel runs where both apply -- 0 (default) chooses by shape, 1 always the shared-memory
- * ring kernel, 2 always the register-streaming kernel. */
+ * fp16 decode kernel runs where both apply -- 0 (default) and 1 the shared-memory ring kernel, 2 the
+ * register-streaming kernel (faster for an isolated large matrix at batch 1-2, slower inside a chain of
+ * dependent launches). */
 void cb_set_option(int option, int value);
 
 /* Synchronises the device, then returns in *status the decode kernels' error word and clears it:

@@ -145,11 +145,11 @@ int run_decode(const char* who, const void* x, GemvParams& P, int bits, int64_t 
         P.counters = reinterpret_cast<int*>(scratch);
         P.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kCounterBytes);
     }
-    // Measured on B200: with one or two batch rows the register-streaming kernel is the faster one once every
-    // CTA has several 16-row tiles to stream through; the ring kernel wins on matrices of few rows, where its
-    // single pass overlaps the neighbouring launches, and for larger batches, where every CTA of the register
-    // kernel would stage all B activation rows.
-    const bool direct_first = g_prefer_direct == 1 || (g_prefer_direct < 0 && P.B <= 2 && P.V >= 8192);
+    // The register-streaming kernel is opt-in (cb_set_option(2, 2)).  Measured on B200 it is the faster kernel
+    // for an isolated large matrix at batch 1-2 (22016x4096 W4: 16.1 us against 19.6 us), but inside the
+    // dependent chain of a decode stack, where a launch cannot read its activations before the previous launch
+    // has finished, the ring kernel's step is shorter (1.48 ms against 2.03 ms for the 32-block stack).
+    const bool direct_first = g_prefer_direct == 1;
     if (!g_force_generic && !g_no_direct && direct_first) {
         // the register-streaming fp16 kernel when the problem is inside its domain (-1 = it is not)
         const int rc = launch_gemv_direct(bits, dtype, x, P, pdl_enabled(), stream);

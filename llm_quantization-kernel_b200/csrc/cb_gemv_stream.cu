@@ -464,6 +464,9 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
     CB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
         CB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemCap));
+        // every decode kernel asks for the same shared-memory carve-out, so that consecutive launches of a stream
+        // never make an SM drain to re-partition its L1 / shared memory
+        CB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg{};
