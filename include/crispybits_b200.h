@@ -189,14 +189,17 @@ size_t cb_gemv_scratch_bytes(int64_t B, int64_t V, int64_t split_k);
  * value 1 forces the shape-generic decode kernel everywhere (for A/B checks).  option 2: which
  * fp16 decode kernel runs where both apply -- 0 (default) and 1 the shared-memory ring kernel, 2 the
  * register-streaming kernel (faster for an isolated large matrix at batch 1-2, slower inside a chain of
- * dependent launches). */
+ * dependent launches).  option 3: which tcgen05 prefill kernel -- 0 (default) by M, 1 the kernel with both
+ * operands in shared memory (128-token tiles), 2 the kernel with the expanded weights in tensor memory
+ * (256-token tiles). */
 void cb_set_option(int option, int value);
 
 /* Synchronises the device, then returns in *status the decode kernels' error word and clears it:
  * 0 = no problem; 0 < k < 1000 = in a decode kernel a shared-memory copy of pass k-1 did not arrive
- * within the wait limit and the affected outputs were not written; 1000 + r = in the tensor-core GEMM
- * role r (1 TMA producer, 2 MMA issuer, 3 dequantiser, 4 epilogue) gave up a bounded wait.  No
- * counterpart in the reference. */
+ * within the wait limit and the affected outputs were not written; 1000 + r (2000 + r for the
+ * weights-in-TMEM kernel) = in the tensor-core GEMM role r (1 activation producer, 2 MMA issuer,
+ * 3 dequantiser, 4 epilogue, 5 packed-word producer) gave up a bounded wait.  No counterpart in the
+ * reference. */
 int cb_decode_status(int* status);
 
 /* Introspection used by the Split-K policy (packed_gemv.cu:339-347; bindings.cpp:37-39). */

@@ -43,6 +43,9 @@ int stream_status_read_and_clear(int* out);
 int launch_peer_wait(const GemvParams& P, cudaStream_t stream);
 int launch_peer_signal(const GemvParams& P, cudaStream_t stream);
 int gemm_status_read_and_clear(int* out);
+int gemm_ws_status_read_and_clear(int* out);
+int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
+                   int64_t gs, int act, cudaStream_t stream);
 int launch_gemm_tc(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
                    int64_t gs, int act, cudaStream_t stream);
 
@@ -57,6 +60,7 @@ bool pdl_enabled() {
 }
 static int g_force_generic = 0;
 static int g_no_direct = 0;
+static int g_gemm_kernel = 0;      // 0: by M, 1: shared-memory-operand kernel, 2: weights-in-TMEM kernel
 static int g_prefer_direct = -1;   // -1: by shape, 1: wherever it applies
 
 int launch_unpack(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, cudaStream_t stream);
@@ -196,6 +200,7 @@ void cb_set_option(int option, int value) {
     if (option == 0) g_pdl = value ? 1 : 0;
     if (option == 1) g_force_generic = value ? 1 : 0;
     if (option == 2) { g_no_direct = value == 1 ? 1 : 0; g_prefer_direct = value == 2 ? 1 : -1; }
+    if (option == 3) g_gemm_kernel = (value == 1 || value == 2) ? value : 0;
 }
 
 int cb_decode_status(int* status) {
@@ -205,7 +210,10 @@ int cb_decode_status(int* status) {
     if (rc != CB_OK) return rc;
     rc = gemm_status_read_and_clear(&b);
     if (rc != CB_OK) return rc;
-    *status = a != 0 ? a : (b != 0 ? 1000 + b : 0);
+    int c = 0;
+    rc = gemm_ws_status_read_and_clear(&c);
+    if (rc != CB_OK) return rc;
+    *status = a != 0 ? a : (b != 0 ? 1000 + b : (c != 0 ? 2000 + c : 0));
     return CB_OK;
 }
 int cb_tile_n(void) { return kTileN; }
@@ -371,7 +379,12 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out, int6
     CB_REQUIRE(out != nullptr, "packed_gemm: out is NULL");
     CB_REQUIRE(M < (1ll << 30), "packed_gemm: M out of range");
     if (use_tensor_cores && !g_force_generic) {
-        // tcgen05 kernel when the problem is inside its domain (-1 = it is not)
+        // tcgen05 kernels when the problem is inside their domain (-1 = it is not): above 128 tokens the one that
+        // keeps the expanded weights in tensor memory and serves 256 tokens per expansion, else the 128-token one
+        if (g_gemm_kernel == 2 || (g_gemm_kernel == 0 && M > 128)) {
+            const int rc3 = launch_gemm_ws(dtype, x, M, w, out, K, bits, group_size, act, reinterpret_cast<cudaStream_t>(stream));
+            if (rc3 != -1) return rc3;
+        }
         const int rc2 = launch_gemm_tc(dtype, x, M, w, out, K, bits, group_size, act, reinterpret_cast<cudaStream_t>(stream));
         if (rc2 != -1) return rc2;
     }

@@ -1,0 +1,531 @@
+// Prefill GEMM on tcgen05 with the dequantised weights held in tensor memory ("weight-stationary").
+//
+//   out[M, N] = act( x[M, K] * Wdq[N, K]^T + bias ),   Wdq = round_fp16((q - zero) * scale)
+//
+// Same numerics as the shared-memory-operand kernel (Crispybits/Kernel/csrc/packed_gemm.cu:47-61: weight
+// rounded to the storage type before the product, fp32 accumulation).  What differs is where the expanded
+// weights live.  With both MMA operands in shared memory, one SM's shared-memory port carries the TMA
+// writes of x, the dequantisers' stores, and the tensor core's reads of both operands -- about 135 KB per
+// 64-code stage, which at 128 bytes per cycle is as long as the MMAs themselves and was measured to bound
+// the kernel.  Here the product is computed transposed, D[n, m] = sum_k Wdq[n, k] * x[m, k]:
+//   * the weight tile is the A operand and is read from TENSOR MEMORY: the dequantiser of weight row n
+//     writes its fp16 values with tcgen05.st into TMEM lane n -- they never touch shared memory;
+//   * the activation tile (256 tokens x 64 codes, TMA, 128-byte swizzle) is the B operand from shared memory;
+//   * the accumulator is 128 weight rows (lanes) x 256 tokens (columns) of fp32 in TMEM, so each packed word is
+//     expanded once per 256 tokens.
+// TMEM map (512 columns): [0, 256) accumulator, [256 + 32 s, 256 + 32 s + 32) A stage s (64 fp16 per lane).
+//
+// One persistent CTA per SM, 23 warps: warp 0 TMA producer of x; warp 1 TMEM owner and MMA issuer
+// (kind::f16, 128 x 256 x 16, four per stage); warps 2-17 dequantisers (TMEM lane quadrant = warp % 4, the
+// four warps of a quadrant take 16 codes each of the stage's 64); warps 18-21 epilogue (tcgen05.ld of their
+// quadrant, bias, activation, fp16 stores: lane = weight row, so the 32 lanes of a store are 64 contiguous
+// bytes of one token's output row); warp 22 TMA producer of the packed words (128 rows x 128 codes per box).
+// Every mbarrier wait is bounded; a wait that runs out raises a flag in shared memory and in the status word,
+// every role leaves its loops, TMEM is released, and the kernel returns.
+#include <algorithm>
+
+#include <cuda.h>
+
+#include "cb_common.cuh"
+
+namespace cb {
+namespace {
+
+constexpr int kBN = 128;                            // weight rows per tile (UMMA M)
+constexpr int kBT = 256;                            // tokens per tile (UMMA N)
+constexpr int kBK = 64;                             // codes per stage
+constexpr int kStages = 6;
+constexpr int kPackedSlots = 3;                     // ring of packed super-blocks (128 codes = two stages each)
+constexpr int kThreads = 23 * 32;
+constexpr int kDequantWarps = 16, kFirstDequantWarp = 2, kFirstEpiWarp = 18, kPackedWarp = 22;
+constexpr uint32_t kXBytes = kBT * kBK * 2;         // 32 KB: one stage of activations
+constexpr uint32_t kPackedSlotBytes = kBN * 64;     // 128 rows x 128 codes at 4 bits; narrower rows use less of it
+constexpr uint32_t kSmemBytes = kStages * kXBytes + kPackedSlots * kPackedSlotBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t kAccCols = 256, kAStageCols = 32;
+constexpr long long kWaitCycles = 2000000000ll;     // about a second at boost clock
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kBT >> 3) << 17) | ((uint32_t)(kBN >> 4) << 24);   // f16 x f16 -> f32, K-major A and B
+
+__device__ int g_gemm_ws_status;   // 0 = ok, else the role that gave up waiting (1 x producer, 2 mma, 3 dequant, 4 epilogue, 5 packed producer)
+
+struct GemmParams {
+    const __half* scales; const __half* zeros; const __half* bias; __half* out;
+    int M, N, K, groups, group_size, act;
+    int tiles_m, tiles_n, kblocks;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns = 20000u) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the phase did not complete in time or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag != 0 || clock64() - t0 > kWaitCycles) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2mul(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+constexpr uint32_t kMagic = 0x64006400u;
+
+// Dequantise 16 consecutive codes of one row into eight half2 registers (codes 2j, 2j+1 in t[j]).  `w` holds the
+// codes as a bit stream that starts at bit 0 of w[0].  Both fields of a pair are masked in place from a copy of
+// their byte(s): (field | 0x6400) reads as 1024 + code * 2^p, one fused multiply-add with 2^-p and
+// -(1024 * 2^-p + zero) leaves code - zero exactly, one multiply applies the scale (a single rounding of the
+// exact product, i.e. the fp16 rounding of the fp32 value the reference rounds).
+template <int BITS> struct Dequant16;
+
+template <> struct Dequant16<4> {
+    __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t zz, uint32_t ss, uint32_t (&t)[8]) {
+        const uint32_t add = h2sub(0xD400E400u, zz);                 // (-1024 - z, -64 - z)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = __byte_perm(w[j >> 2], 0u, (j & 3) | ((j & 3) << 8));   // byte -> bytes 0 and 2
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = lop3_and_or(t[j], 0x00F0000Fu, kMagic);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = h2fma(t[j], 0x2C003C00u, add);                          // * (1, 1/16)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = h2mul(t[j], ss);
+    }
+};
+
+template <> struct Dequant16<2> {
+    __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t zz, uint32_t ss, uint32_t (&t)[8]) {
+        const uint32_t add01 = h2sub(0xDC00E400u, zz);               // (-1024 - z, -256 - z)   fields at bits 0, 2
+        const uint32_t add23 = h2sub(0xCC00D400u, zz);               // (-64 - z,  -16 - z)     fields at bits 4, 6
+        uint32_t b[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = __byte_perm(w[0], 0u, j | (j << 8));                    // byte j = codes 4j..4j+3
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            t[2 * j] = lop3_and_or(b[j], 0x000C0003u, kMagic);
+            t[2 * j + 1] = lop3_and_or(b[j], 0x00C00030u, kMagic);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            t[2 * j] = h2fma(t[2 * j], 0x34003C00u, add01);                                          // * (1, 1/4)
+            t[2 * j + 1] = h2fma(t[2 * j + 1], 0x24002C00u, add23);                                  // * (1/16, 1/64)
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = h2mul(t[j], ss);
+    }
+};
+
+template <> struct Dequant16<3> {
+    __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t zz, uint32_t ss, uint32_t (&t)[8]) {
+        const uint32_t add = h2sub(0xE400E400u, zz);                 // (-1024 - z) twice
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {                                // codes 2j, 2j+1 at stream bit 6j (48 bits in all)
+            const int pos = 6 * j, wi = pos >> 5, off = pos & 31;
+            if (off + 6 <= 32) t[j] = w[wi] >> off;
+            else t[j] = __funnelshift_r(w[0], w[1], off);            // the pair that straddles the two words
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = (t[j] & 0x3Fu) * 0x2001u;   // low code stays at bit 0, high code moves to bit 16
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = lop3_and_or(t[j], 0x00070007u, kMagic);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = h2fma(t[j], 0x3C003C00u, add);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = h2mul(t[j], ss);
+    }
+};
+
+template <int BITS>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const GemmParams P) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                    // swizzled tiles want 1024-byte alignment
+    unsigned char* smem = smem_raw + (base - raw);
+    constexpr uint32_t kPackedOff = kStages * kXBytes;
+    constexpr uint32_t kBarOff = kPackedOff + kPackedSlots * kPackedSlotBytes;
+    constexpr int kWords = 2 * BITS;                                 // packed words of one row and stage (64 codes)
+    constexpr uint32_t kRowBytes = 2 * kWords * 4;                   // one row of a packed super-block (128 codes)
+    const uint32_t s_bar = base + kBarOff;
+    // barriers: full_x[s], full_w[s], empty[s], tmem_full, tmem_empty, full_p[slot], empty_p[slot]
+    auto full_x = [&](int s) { return s_bar + 8u * s; };
+    auto full_w = [&](int s) { return s_bar + 8u * (kStages + s); };
+    auto empty = [&](int s) { return s_bar + 8u * (2 * kStages + s); };
+    const uint32_t tmem_full = s_bar + 8u * (3 * kStages), tmem_empty = s_bar + 8u * (3 * kStages + 1);
+    auto full_p = [&](int s) { return s_bar + 8u * (3 * kStages + 2 + s); };
+    auto empty_p = [&](int s) { return s_bar + 8u * (3 * kStages + 2 + kPackedSlots + s); };
+    constexpr uint32_t kNumBars = 3 * kStages + 2 + 2 * kPackedSlots;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kBarOff + 8 * kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kBarOff + 8 * kNumBars + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_x(s), 1);
+            mbar_init(full_w(s), 4);                 // the four warps (lane quadrants) of one dequantiser group
+            mbar_init(empty(s), 1);
+        }
+        mbar_init(tmem_full, 1);
+        mbar_init(tmem_empty, 4);
+        for (int s = 0; s < kPackedSlots; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kDequantWarps); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // all 512 TMEM columns: the accumulator and the weight stages
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32((const void*)tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int ntiles = P.tiles_m * P.tiles_n;
+    const int nsuper = (P.kblocks + 1) >> 1;                         // packed super-blocks per tile
+    int gave_up = 0;
+
+#ifdef CB_WS_BARE
+    const bool bare = true;      // diagnostic build: only the MMA issuer and the epilogue run
+#else
+    const bool bare = false;
+#endif
+    if (bare && warp != 1 && (warp < kFirstEpiWarp || warp == kPackedWarp)) {
+        // nothing
+    } else if (warp == 0) {
+        // ================= TMA producer: activation tiles, 256 tokens x 64 codes =================
+        if (lane == 0) {
+            int it = 0;
+            for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x) {
+                const int m0 = (tile % P.tiles_m) * kBT;
+                for (int kb = 0; kb < P.kblocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (it >= kStages && !mbar_wait(empty(s), ((it / kStages) - 1) & 1, abort_flag)) { gave_up = 1; break; }
+                    mbar_expect_tx(full_x(s), kXBytes);
+                    tma_load_2d(base + s * kXBytes, &xmap, kb * kBK, m0, full_x(s));
+                }
+            }
+        }
+    } else if (warp == kPackedWarp) {
+        // ================= TMA producer: packed words, 128 rows x 128 codes per box =================
+        if (lane == 0) {
+            int pit = 0;
+            for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x) {
+                const int n0 = (tile / P.tiles_m) * kBN;
+                for (int sb = 0; sb < nsuper; ++sb, ++pit) {
+                    const int slot = pit % kPackedSlots;
+                    if (pit >= kPackedSlots && !mbar_wait(empty_p(slot), ((pit / kPackedSlots) - 1) & 1, abort_flag)) { gave_up = 5; break; }
+                    mbar_expect_tx(full_p(slot), kBN * kRowBytes);
+                    tma_load_2d(base + kPackedOff + slot * kPackedSlotBytes, &wmap, sb * 2 * kWords, n0, full_p(slot));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer: A (weights) from tensor memory, B (activations) from shared memory =================
+        if (lane == 0) {
+            int it = 0, tcount = 0;
+            for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x, ++tcount) {
+                // the one accumulator must have been drained by the epilogue of the previous tile
+                if (tcount >= 1 && !mbar_wait(tmem_empty, (tcount - 1) & 1, abort_flag)) { gave_up = 2; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int kb = 0; kb < P.kblocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+#ifndef CB_WS_BARE
+                    if (!mbar_wait(full_x(s), ph, abort_flag) || !mbar_wait(full_w(s), ph, abort_flag)) { gave_up = 2; break; }
+#else
+                    (void)ph;
+#endif
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t xa = base + s * kXBytes;
+                    const uint32_t a_tmem = tmem_base + kAccCols + (uint32_t)s * kAStageCols;
+                    // B descriptor: K-major, 128-byte swizzle, 8-row atoms 1024 bytes apart
+                    const uint64_t dhi = (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        const uint64_t bdesc = dhi | (uint64_t)(((xa + k * 32) >> 4) & 0x3FFF);
+                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                                     " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}"
+                                     ::"r"(tmem_base), "r"(a_tmem + (uint32_t)k * 8u), "l"(bdesc), "r"(kIdesc), "r"(accumulate), "r"(0u) : "memory");
+                    }
+                    // the stage (shared-memory x tile and TMEM weight columns) may be refilled once these MMAs have read it
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(empty(s)) : "memory");
+                }
+                if (gave_up) break;
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tmem_full) : "memory");
+            }
+        }
+    } else if (warp < kFirstEpiWarp) {
+        // ================= dequantisers: four groups of four warps; group g expands stages g, g+4, g+8, ... =================
+        // A stage's hand-off chain (packed words landed -> expand -> TMEM store -> signal) is several hundred cycles
+        // long; with every group on its own stage four such chains overlap, and a group has four stage times to
+        // finish one.  Within a group, warp = TMEM lane quadrant, lane = weight row: a thread expands all 64 codes
+        // of its row and stage and writes them to its TMEM lane with one 32-column store.
+        const int q = warp & 3;                                           // the TMEM lane quadrant this warp may access
+        const int grp = (warp - kFirstDequantWarp) >> 2;                  // 0..3
+        const int r = q * 32 + lane;                                      // weight row of the tile = TMEM lane
+        const int my_tiles = blockIdx.x < ntiles ? (ntiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+        const int total = my_tiles * P.kblocks;                           // stages this CTA runs through
+        const unsigned short* srow = nullptr;
+        const unsigned short* zrow = nullptr;
+        int cur_tile_local = -1;
+        bool live = false;
+        auto meta_of = [&](int it) -> uint32_t {                          // (zero << 16) | scale of (row, stage it), raw fp16 bits
+            if (it >= total) return 0u;
+            const int tl = it / P.kblocks, kb = it - tl * P.kblocks;
+            if (tl != cur_tile_local) {
+                cur_tile_local = tl;
+                const int tile = blockIdx.x + tl * gridDim.x;
+                const int n = (tile / P.tiles_m) * kBN + r;
+                live = n < P.N;
+                srow = reinterpret_cast<const unsigned short*>(P.scales) + (size_t)(live ? n : 0) * P.groups;
+                zrow = reinterpret_cast<const unsigned short*>(P.zeros) + (size_t)(live ? n : 0) * P.groups;
+            }
+            if (!live) return 0u;                                         // rows past N were zero-filled by the copy and get scale 0
+            const int g = (kb * kBK) / P.group_size;
+            return (uint32_t)__ldg(srow + g) | ((uint32_t)__ldg(zrow + g) << 16);
+        };
+        // Every group passes every packed super-block in order (wait for it, read its own stage's words if it has
+        // one there, release it): each mbarrier phase is then observed exactly once by each waiter, which is what
+        // the parity protocol needs.  Stage index = 2 * super-block + half; group = stage index mod 4.
+        const int total_super = total >> 1;                               // kblocks is even
+        uint32_t meta_next = meta_of(grp);
+        for (int pit = 0; pit < total_super && !gave_up; ++pit) {
+            const int slot = pit % kPackedSlots;
+            if (!__all_sync(0xffffffffu, mbar_wait(full_p(slot), (pit / kPackedSlots) & 1, abort_flag))) { gave_up = 3; break; }
+            const int half = ((2 * pit) & 3) == grp ? 0 : (((2 * pit + 1) & 3) == grp ? 1 : -1);
+            uint32_t w[kWords];
+            if (half >= 0) {
+                const unsigned char* stage_words = smem + kPackedOff + slot * kPackedSlotBytes + (uint32_t)r * kRowBytes + half * (kWords * 4);
+                if constexpr (BITS == 4) {
+                    const uint4 a = reinterpret_cast<const uint4*>(stage_words)[0], b4 = reinterpret_cast<const uint4*>(stage_words)[1];
+                    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b4.x; w[5] = b4.y; w[6] = b4.z; w[7] = b4.w;
+                } else if constexpr (BITS == 2) {
+                    const uint4 a = reinterpret_cast<const uint4*>(stage_words)[0];
+                    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+                } else {
+                    const uint2 a = reinterpret_cast<const uint2*>(stage_words)[0], b2 = reinterpret_cast<const uint2*>(stage_words)[1],
+                                c2 = reinterpret_cast<const uint2*>(stage_words)[2];
+                    w[0] = a.x; w[1] = a.y; w[2] = b2.x; w[3] = b2.y; w[4] = c2.x; w[5] = c2.y;
+                }
+            }
+            // this warp is done with the packed slot (16 arrivals per slot: every dequantiser warp)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_p(slot));
+            if (half < 0) continue;
+            const int it = 2 * pit + half;
+            const int s = it % kStages;
+            const uint32_t meta = meta_next;
+            meta_next = meta_of(it + 4);                                  // requested one of this group's stages ahead
+            const uint32_t ss = (meta & 0xFFFFu) * 0x10001u, zz = (meta >> 16) * 0x10001u;
+            uint32_t t[32];
+#pragma unroll
+            for (int kq = 0; kq < 4; ++kq) {                              // 16 codes at a time
+                uint32_t w2[2];
+                if constexpr (BITS == 4) { w2[0] = w[2 * kq]; w2[1] = w[2 * kq + 1]; }
+                else if constexpr (BITS == 2) { w2[0] = w[kq]; w2[1] = 0u; }
+                else {
+                    // 48 bits from stream bit 48 * kq: two words, shifted down by 16 for odd quarters
+                    const uint32_t lo = w[(3 * kq) >> 1], hi = w[((3 * kq) >> 1) + 1];
+                    w2[0] = (kq & 1) ? __funnelshift_r(lo, hi, 16) : lo;
+                    w2[1] = (kq & 1) ? (hi >> 16) : hi;
+                }
+                uint32_t t8[8];
+                Dequant16<BITS>::run(w2, zz, ss, t8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t[8 * kq + j] = t8[j];
+            }
+            if (it >= kStages && !__all_sync(0xffffffffu, mbar_wait(empty(s), ((it / kStages) - 1) & 1, abort_flag))) { gave_up = 3; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // lane r, the 32 columns of A stage s: codes 2c, 2c+1 of this stage in column c
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + kAccCols + (uint32_t)s * kAStageCols;
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                         "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                         ::"r"(taddr), "r"(t[0]), "r"(t[1]), "r"(t[2]), "r"(t[3]), "r"(t[4]), "r"(t[5]), "r"(t[6]), "r"(t[7]),
+                           "r"(t[8]), "r"(t[9]), "r"(t[10]), "r"(t[11]), "r"(t[12]), "r"(t[13]), "r"(t[14]), "r"(t[15]),
+                           "r"(t[16]), "r"(t[17]), "r"(t[18]), "r"(t[19]), "r"(t[20]), "r"(t[21]), "r"(t[22]), "r"(t[23]),
+                           "r"(t[24]), "r"(t[25]), "r"(t[26]), "r"(t[27]), "r"(t[28]), "r"(t[29]), "r"(t[30]), "r"(t[31]) : "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_w(s));
+        }
+    } else if (warp < kPackedWarp) {
+        // ================= epilogue: TMEM -> registers -> global (lane = weight row, column = token) =================
+        const int q = warp & 3;                                       // the TMEM lane quadrant this warp may read
+        int tcount = 0;
+        for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x, ++tcount) {
+            const int m0 = (tile % P.tiles_m) * kBT;
+            const int n = (tile / P.tiles_m) * kBN + q * 32 + lane;
+            if (!__all_sync(0xffffffffu, mbar_wait(tmem_full, tcount & 1, abort_flag))) { gave_up = 4; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+            const bool nlive = n < P.N;
+            const float bias = (nlive && P.bias != nullptr) ? __half2float(P.bias[n]) : 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kBT; c0 += 32) {
+                uint32_t v[32];
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                               "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                               "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                               "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                             : "r"(taddr + (uint32_t)c0));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (nlive) {
+                    __half* ocol = P.out + (size_t)(m0 + c0) * P.N + n;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (m0 + c0 + j < P.M)
+                            ocol[(size_t)j * P.N] = __float2half_rn(activate(__uint_as_float(v[j]) + bias, P.act));
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty);
+        }
+    }
+
+    if (gave_up) {
+        *abort_flag = 1;
+        atomicExch(&g_gemm_ws_status, gave_up);
+    }
+    // everyone is done with TMEM before it is released
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+template <int BITS>
+int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const GemmParams& P, int grid, cudaStream_t stream) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    CB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        CB_CUDA_TRY(cudaFuncSetAttribute(gemm_ws_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    gemm_ws_kernel<BITS><<<grid, kThreads, kSmemBytes, stream>>>(xmap, wmap, P);
+    CB_CUDA_TRY(cudaGetLastError());
+    return CB_OK;
+}
+
+}  // namespace
+
+// CB_OK after launching; a CB_ERR_* code on a CUDA error; -1 when the problem is outside this kernel's
+// domain (fp16, K a multiple of 128, group size a multiple of 64, N a multiple of 8, 16-byte aligned
+// x / packed / out) and the caller should use another kernel.
+int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
+                   int64_t gs, int act, cudaStream_t stream) {
+    if (dtype != CB_F16 || K % 128 != 0 || gs % kBK != 0 || w->n % 8 != 0 || M < 1) return -1;
+    if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(w->packed) % 16 ||
+        reinterpret_cast<uintptr_t>(out) % 16)
+        return -1;
+    if (M >= (1ll << 31) / 2 || K >= (1ll << 30)) return -1;
+    EncodeTiledFn enc = encode_fn();
+    if (enc == nullptr) return -1;
+    const int sms = sm_count_current();
+    if (sms <= 0) return CB_ERR_CUDA;
+
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap xmap, wmap;
+    {   // activations: [M, K] fp16, box 64 x 256, 128-byte swizzle (the UMMA K-major layout)
+        const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+        const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+        const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBT};
+        const CUresult cr = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) { set_error("packed_gemm: cuTensorMapEncodeTiled(x) failed (%d)", (int)cr); return CB_ERR_CUDA; }
+    }
+    {   // packed words: [N, K/32*bits] uint32, box (128 codes) x 128 rows, no swizzle
+        const cuuint64_t wpr = (cuuint64_t)(K / 32) * bits;
+        const cuuint64_t dims[2] = {wpr, (cuuint64_t)w->n};
+        const cuuint64_t strides[1] = {wpr * 4};
+        const cuuint32_t box[2] = {(cuuint32_t)(4 * bits), (cuuint32_t)kBN};
+        const CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<int32_t*>(w->packed), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) { set_error("packed_gemm: cuTensorMapEncodeTiled(packed) failed (%d)", (int)cr); return CB_ERR_CUDA; }
+    }
+
+    GemmParams P{};
+    P.scales = reinterpret_cast<const __half*>(w->scales);
+    P.zeros = reinterpret_cast<const __half*>(w->zeros);
+    P.bias = reinterpret_cast<const __half*>(w->bias);
+    P.out = reinterpret_cast<__half*>(out);
+    P.M = (int)M; P.N = (int)w->n; P.K = (int)K;
+    P.groups = (int)((K + gs - 1) / gs); P.group_size = (int)gs; P.act = act;
+    P.tiles_m = (int)((M + kBT - 1) / kBT); P.tiles_n = (int)((w->n + kBN - 1) / kBN); P.kblocks = (int)(K / kBK);
+    const int grid = std::min(sms, P.tiles_m * P.tiles_n);
+    switch (bits) {
+        case 2: return launch_t<2>(xmap, wmap, P, grid, stream);
+        case 3: return launch_t<3>(xmap, wmap, P, grid, stream);
+        default: return launch_t<4>(xmap, wmap, P, grid, stream);
+    }
+}
+
+int gemm_ws_status_read_and_clear(int* out) {
+    int v = 0, zero = 0;
+    CB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_gemm_ws_status, sizeof(int)));
+    CB_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_ws_status, &zero, sizeof(int)));
+    *out = v;
+    return CB_OK;
+}
+
+}  // namespace cb

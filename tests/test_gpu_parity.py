@@ -300,6 +300,17 @@ def test_prefill_gemm_tensor_core_kernel(bits, M, n, k):
     finally:
         _C.set_option(1, 0)
     assert rel_err(y, slow.float()) < 1e-3
+    # both tcgen05 kernels on the same call: operands in shared memory (1), expanded weights in tensor memory (2)
+    both = []
+    try:
+        for which in (1, 2):
+            _C.set_option(3, which)
+            both.append(packed_linear(x, w, act="silu", decode_threshold=0))
+    finally:
+        _C.set_option(3, 0)
+    for o in both:
+        assert rel_err(o, rounded) < 1e-3
+    assert rel_err(both[0], both[1].float()) < 2e-4      # same products, different summation order inside the MMA
     assert _C.decode_status() == 0
 
 
