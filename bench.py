@@ -470,12 +470,13 @@ def reduce_sum(v):
 
 
 def bench_gemm(device, tf_peak, peak_kind, m=1024, iters=10):
-    """Prefill GEMM at M=1024 over the 4096x4096 W4 and W3 matrices (TFLOP/s = 2*M*N*K / t)."""
+    """Prefill GEMM at M=1024 (TFLOP/s = 2*M*N*K / t): the 4096x4096 matrix at W4 and W3, and at W4 the other
+    three (N, K) shapes of the prefill configuration."""
     import crispybits_kernels as ck
     out = {}
-    x = torch.randn(m, K_IN, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(5))
-    for b in (4, 3):
-        ws = device_copies(synth_weight_numpy(b, b), device, 2)
+    for (n, k, b) in ((N_OUT, K_IN, 4), (N_OUT, K_IN, 3), (12288, 4096, 4), (22016, 4096, 4), (4096, 11008, 4)):
+        x = torch.randn(m, k, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(5))
+        ws = device_copies(synth_weight_numpy(b, b, n, k), device, 2)
         for _ in range(3):
             ck.packed_linear(x, ws[0])
         torch.cuda.synchronize()
@@ -486,9 +487,10 @@ def bench_gemm(device, tf_peak, peak_kind, m=1024, iters=10):
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / iters
-        tf = 2.0 * m * N_OUT * K_IN / (us * 1e-6) / 1e12
-        out[f"m{m}_4096x4096_w{b}"] = {"us": us, "tflops": tf, "frac_of_dense_peak": tf / tf_peak,
-                                       "peak_kind": f"of {peak_kind}"}
+        tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
+        out[f"m{m}_{n}x{k}_w{b}"] = {"us": us, "tflops": tf, "frac_of_dense_peak": tf / tf_peak,
+                                     "peak_kind": f"of {peak_kind}"}
+        del ws, x
     return out
 
 

@@ -35,7 +35,7 @@ constexpr int kBN = 128;                            // weight rows per tile (UMM
 constexpr int kBT = 256;                            // tokens per tile (UMMA N)
 constexpr int kBK = 64;                             // codes per stage
 constexpr int kStages = 6;
-constexpr int kPackedSlots = 3;                     // ring of packed super-blocks (128 codes = two stages each)
+constexpr int kPackedSlots = 4;                     // ring of packed super-blocks (128 codes = two stages each)
 constexpr int kThreads = 23 * 32;
 constexpr int kDequantWarps = 16, kFirstDequantWarp = 2, kFirstEpiWarp = 18, kPackedWarp = 22;
 constexpr uint32_t kXBytes = kBT * kBK * 2;         // 32 KB: one stage of activations
@@ -221,7 +221,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 #else
     const bool bare = false;
 #endif
-    if (bare && warp != 1 && (warp < kFirstEpiWarp || warp == kPackedWarp)) {
+#if defined(CB_WS_BARE) && CB_WS_BARE == 2
+    const bool with_x = true;
+#else
+    const bool with_x = false;
+#endif
+    if (bare && warp != 1 && !(with_x && warp == 0) && (warp < kFirstEpiWarp || warp == kPackedWarp)) {
         // nothing
     } else if (warp == 0) {
         // ================= TMA producer: activation tiles, 256 tokens x 64 codes =================
@@ -239,7 +244,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         }
     } else if (warp == kPackedWarp) {
         // ================= TMA producer: packed words, 128 rows x 128 codes per box =================
+#if defined(CB_WS_DIAG) && (CB_WS_DIAG & 2)
+        if (false) {                                  // diagnostic: no packed-word traffic
+#else
         if (lane == 0) {
+#endif
             int pit = 0;
             for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x) {
                 const int n0 = (tile / P.tiles_m) * kBN;
@@ -264,6 +273,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     const uint32_t ph = (it / kStages) & 1;
 #ifndef CB_WS_BARE
                     if (!mbar_wait(full_x(s), ph, abort_flag) || !mbar_wait(full_w(s), ph, abort_flag)) { gave_up = 2; break; }
+#elif CB_WS_BARE == 2
+                    if (!mbar_wait(full_x(s), ph, abort_flag)) { gave_up = 2; break; }     // diagnostic: activations only
 #else
                     (void)ph;
 #endif
@@ -324,7 +335,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         uint32_t meta_next = meta_of(grp);
         for (int pit = 0; pit < total_super && !gave_up; ++pit) {
             const int slot = pit % kPackedSlots;
+#if !(defined(CB_WS_DIAG) && (CB_WS_DIAG & 2))
             if (!__all_sync(0xffffffffu, mbar_wait(full_p(slot), (pit / kPackedSlots) & 1, abort_flag))) { gave_up = 3; break; }
+#endif
             const int half = ((2 * pit) & 3) == grp ? 0 : (((2 * pit + 1) & 3) == grp ? 1 : -1);
             uint32_t w[kWords];
             if (half >= 0) {
@@ -341,10 +354,16 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     w[0] = a.x; w[1] = a.y; w[2] = b2.x; w[3] = b2.y; w[4] = c2.x; w[5] = c2.y;
                 }
             }
-            // this warp is done with the packed slot (16 arrivals per slot: every dequantiser warp)
+            // A warp that has no stage in this super-block hands the slot back at once; a warp that has one hands it
+            // back only after its stage is in tensor memory (below).  Handing it back right after the loads were
+            // issued was measured to be unsafe: in a few percent of runs (in all runs once the dequantisers were
+            // slowed down artificially) rows were expanded from a mixture of this super-block and the one that the
+            // next TMA box brought into the slot.
             __syncwarp();
-            if (lane == 0) mbar_arrive(empty_p(slot));
-            if (half < 0) continue;
+            if (half < 0) {
+                if (lane == 0) mbar_arrive(empty_p(slot));
+                continue;
+            }
             const int it = 2 * pit + half;
             const int s = it % kStages;
             const uint32_t meta = meta_next;
@@ -363,7 +382,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     w2[1] = (kq & 1) ? (hi >> 16) : hi;
                 }
                 uint32_t t8[8];
+#if defined(CB_WS_DIAG) && (CB_WS_DIAG & 1)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t8[j] = w2[j & 1] ^ zz ^ ss;      // diagnostic: no unpack arithmetic
+#else
                 Dequant16<BITS>::run(w2, zz, ss, t8);
+#endif
 #pragma unroll
                 for (int j = 0; j < 8; ++j) t[8 * kq + j] = t8[j];
             }
@@ -381,7 +405,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(full_w(s));
+            if (lane == 0) { mbar_arrive(full_w(s)); mbar_arrive(empty_p(slot)); }
         }
     } else if (warp < kPackedWarp) {
         // ================= epilogue: TMEM -> registers -> global (lane = weight row, column = token) =================

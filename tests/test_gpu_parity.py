@@ -314,6 +314,31 @@ def test_prefill_gemm_tensor_core_kernel(bits, M, n, k):
     assert _C.decode_status() == 0
 
 
+@pytest.mark.parametrize("M,n,k", [(300, 4096, 4096), (1024, 1000, 11008)])
+def test_prefill_gemm_is_stable_over_repeated_launches(M, n, k):
+    """Shapes with fewer tiles than SMs, where the kernel's roles run at other relative speeds than in the large
+    cases, launched 150 times: every launch reproduces the first one bit for bit and agrees with the CUDA-core
+    kernel.  (An early version handed shared-memory slots back too soon and failed this in a few percent of runs.)"""
+    from crispybits_kernels import _C, packed_linear
+    w, _, _ = cached(n, k, 4, torch.float16, False, 9, 128, 0.02)
+    x = torch.randn(M, k, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(7))
+    _C.set_option(1, 1)
+    try:
+        slow = packed_linear(x, w, decode_threshold=0)
+    finally:
+        _C.set_option(1, 0)
+    for which in (1, 2):
+        _C.set_option(3, which)
+        try:
+            first = packed_linear(x, w, decode_threshold=0)
+            assert rel_err(first, slow.float()) < 1e-3
+            for _ in range(150):
+                assert torch.equal(packed_linear(x, w, decode_threshold=0), first)
+        finally:
+            _C.set_option(3, 0)
+    assert _C.decode_status() == 0
+
+
 # ------------------------------------------------------------------ fused gate/up and QKV
 @pytest.mark.parametrize("bits", [2, 3, 4])
 @pytest.mark.parametrize("B", [1, 4])
