@@ -157,6 +157,14 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out,
  * exported so that the integer layout can be checked bit-for-bit against the oracle. */
 int cb_unpack_codes(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, void* stream);
 
+/* Quantise and pack on the GPU: the device counterpart of quantize_affine + pack_codes
+ * (Crispybits/Kernel/crispybits_kernels/reference.py:10-27, :37-55), bit-identical to them.  w is [n, K] of
+ * w_dtype (CB_F32 / CB_F16 / CB_BF16, read as fp32); packed receives [n, ceil(K/32)*bits] words, scales and
+ * zeros [n, ceil(K/group_size)] values of meta_dtype (the fp32 results rounded once, as
+ * pack_linear_dict does at reference.py:74).  group_size must be a multiple of 32. */
+int cb_quantize_pack(const void* w, int w_dtype, int64_t n, int64_t K, int bits, int64_t group_size,
+                     int32_t* packed, void* scales, void* zeros, int meta_dtype, void* stream);
+
 /* Decode GEMV with library-owned scratch, for callers that cannot allocate device memory.
  * No counterpart in the reference (its launcher allocates with torch::empty on every call).
  * Same arguments and result as cb_packed_gemv, minus the scratch pair: the Split-K partial sums and

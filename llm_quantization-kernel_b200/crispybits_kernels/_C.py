@@ -399,6 +399,29 @@ def unpack_codes(packed: torch.Tensor, bits: int, in_features: int) -> torch.Ten
     return out
 
 
+_lib.cb_quantize_pack.argtypes = [_vp, _int, _i64, _i64, _int, _i64, _vp, _vp, _vp, _int, _vp]
+_lib.cb_quantize_pack.restype = _int
+
+
+def quantize_pack(w: torch.Tensor, bits: int, group_size: int, meta_dtype=torch.float16):
+    """(packed int32 [N, ceil(K/32)*bits], scales, zeros [N, ceil(K/gs)] of meta_dtype) from a CUDA [N, K] float
+    matrix, computed by the library's quantise+pack kernel (bit-identical to the reference's CPU packer)."""
+    if not w.is_cuda or w.dim() != 2 or w.dtype not in _DTYPE:
+        _fail("quantize_pack: w must be a 2-D CUDA tensor of float32, float16 or bfloat16")
+    if meta_dtype not in _DTYPE:
+        _fail("quantize_pack: scales/zeros dtype must be float32, float16 or bfloat16")
+    bits, gs = int(bits), int(group_size)
+    w = w.contiguous()
+    n, k = w.shape
+    packed = torch.empty((n, -(-k // 32) * bits), dtype=torch.int32, device=w.device)
+    scales = torch.empty((n, -(-k // gs)), dtype=meta_dtype, device=w.device)
+    zeros = torch.empty_like(scales)
+    with torch.cuda.device(w.device):
+        _rc(_lib.cb_quantize_pack(w.data_ptr(), _DTYPE[w.dtype], n, k, bits, gs, packed.data_ptr(), scales.data_ptr(),
+                                  zeros.data_ptr(), _DTYPE[meta_dtype], torch.cuda.current_stream(w.device).cuda_stream))
+    return packed, scales, zeros
+
+
 def sm_count() -> int:
     n = _lib.cb_sm_count()
     if n < 0:

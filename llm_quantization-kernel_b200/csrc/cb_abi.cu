@@ -64,6 +64,8 @@ static int g_gemm_kernel = 0;      // 0: by M, 1: shared-memory-operand kernel, 
 static int g_prefer_direct = -1;   // -1: by shape, 1: wherever it applies
 
 int launch_unpack(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, cudaStream_t stream);
+int launch_quantize_pack(const void* w, int w_dtype, int64_t n, int64_t K, int bits, int64_t gs, int32_t* packed,
+                         void* scales, void* zeros, int meta_dtype, cudaStream_t stream);
 int launch_gemm_simt(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
                      int64_t gs, int act, int round_w, cudaStream_t stream);
 
@@ -399,6 +401,18 @@ int cb_unpack_codes(const int32_t* packed, int64_t n, int64_t K, int bits, int32
     if (n == 0 || K == 0) return CB_OK;
     CB_REQUIRE(packed && codes, "unpack_codes: NULL pointer");
     return launch_unpack(packed, n, K, bits, codes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cb_quantize_pack(const void* w, int w_dtype, int64_t n, int64_t K, int bits, int64_t group_size, int32_t* packed,
+                     void* scales, void* zeros, int meta_dtype, void* stream) {
+    CB_REQUIRE(bits == 2 || bits == 3 || bits == 4, "quantize_pack: bits must be 2/3/4");
+    CB_REQUIRE(n >= 0 && K >= 1 && K < (1ll << 30), "quantize_pack: bad shape");
+    CB_REQUIRE(group_size > 0 && group_size % 32 == 0, "quantize_pack: group_size must be a positive multiple of 32");
+    CB_REQUIRE(w_dtype >= CB_F32 && w_dtype <= CB_BF16 && meta_dtype >= CB_F32 && meta_dtype <= CB_BF16, "quantize_pack: unknown dtype");
+    if (n == 0) return CB_OK;
+    CB_REQUIRE(w && packed && scales && zeros, "quantize_pack: NULL pointer");
+    return launch_quantize_pack(w, w_dtype, n, K, bits, group_size, packed, scales, zeros, meta_dtype,
+                                reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
