@@ -43,19 +43,46 @@ class TuneReport:
         return self.best.ms / self.oracle.ms - 1.0
 
 
+GRAPH_REPS = 16     # calls captured into one CUDA graph when timing on a GPU
+
+
 def _time(fn: Callable[[], object], warmup: int, iters: int) -> float:
-    """Milliseconds per call: CUDA events on the current stream when a GPU is in use, wall clock otherwise."""
+    """Milliseconds per call.  On a GPU the call is captured GRAPH_REPS times into a CUDA graph and the graph is
+    replayed, timed with CUDA events on the current stream: a decode launch is a few microseconds, far below the
+    cost of issuing it from Python, so eager timing would measure the host.  Falls back to eager CUDA-event
+    timing if the capture fails, and to the wall clock without a GPU."""
     for _ in range(warmup):
         fn()
     if torch.cuda.is_available() and torch.cuda.is_initialized():
         torch.cuda.synchronize()
+        graph, reps = None, 1
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                keep = [fn() for _ in range(GRAPH_REPS)]
+            reps = GRAPH_REPS
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception:
+            graph, reps = None, 1
+            torch.cuda.synchronize()
+        rounds = max(1, iters // reps)
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
-        for _ in range(iters):
-            fn()
+        for _ in range(rounds):
+            if graph is not None:
+                graph.replay()
+            else:
+                fn()
         t1.record()
         torch.cuda.synchronize()
-        return t0.elapsed_time(t1) / iters
+        return t0.elapsed_time(t1) / (rounds * reps)
     start = time.perf_counter()
     for _ in range(iters):
         fn()
@@ -87,6 +114,7 @@ def _tune(run: Callable[[int, int], object], B: int, V: int, K: int, bits: int, 
     for rho in range(1, levels + 1):
         measure(rho, candidate_split_k(ceil(B / BATCH_BLOCK), V, bn, sms, rho, max_split), True)
         measure(rho, balanced_split_k(B, V, bn, sms, rho, nchunks), True)
+        measure(rho, 1, True)      # what ops._resolve picks inside the fp16 ring kernel's domain
     if exhaustive:
         for rho in range(1, levels + 1):
             for split in EXHAUSTIVE_PK:

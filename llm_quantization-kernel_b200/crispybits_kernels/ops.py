@@ -224,11 +224,18 @@ def balanced_split_k(batch: int, n: int, bn: int, sms: int, rho: int, nchunks: i
     return best
 
 
-def _resolve(split_k: Optional[int], rho: int, batch: int, v_rows: int, k: int, device) -> int:
+def _resolve(split_k: Optional[int], rho: int, batch: int, v_rows: int, k: int, device,
+             dtype=None, group_size: Optional[int] = None) -> int:
     """An explicit split_k is clamped to the chunk count; None applies the policy for this batch."""
     nchunks = ceil(k / 32)
     if split_k is not None:
         return max(1, min(int(split_k), nchunks))
+    # Inside the domain of the fp16 ring kernel (group 128, K a multiple of 256, up to 8 batch rows) no split is
+    # the measured optimum on B200 at every shape tried, also for 512- and 1376-row shards (3.2 us against 5.0 us
+    # with the underfill rule's split): the kernel spreads a matrix over the SMs by rows and a K split costs it
+    # a partial-sum round trip through memory that is as long as the whole launch.
+    if dtype == torch.float16 and group_size == 128 and k % 256 == 0 and batch <= BATCH_BLOCK:
+        return 1
     if device.type == "cuda":
         index = device.index if device.index is not None else torch.cuda.current_device()
     else:
@@ -251,7 +258,7 @@ def _packed_linear_raw(x, w, split_k=None, rho=1, act=None, decode_threshold=DEC
     x2 = _rows(x)
     code = ACT[act]
     if x2.shape[0] <= decode_threshold:
-        split = _resolve(split_k, rho, x2.shape[0], w.out_features, w.in_features, x2.device)
+        split = _resolve(split_k, rho, x2.shape[0], w.out_features, w.in_features, x2.device, x2.dtype, w.group_size)
         y = _C.packed_gemv(x2, w.packed, w.scales, w.zeros, _bias_arg(w, x2), w.bits, w.in_features,
                            w.group_size, split, rho, code, _ws_arg(workspace, x2))
     else:
@@ -280,7 +287,7 @@ def fused_gate_up(x: torch.Tensor, gate: PackedLinearWeight, up: PackedLinearWei
     x2 = _rows(x)
     if x2.shape[0] <= decode_threshold:
         split = _resolve(split_k, rho, x2.shape[0], virtual_rows("gate_up", gate.out_features),
-                         gate.in_features, x2.device)
+                         gate.in_features, x2.device, x2.dtype, gate.group_size)
         y = _C.fused_gate_up(x2, gate.packed, gate.scales, gate.zeros, up.packed, up.scales, up.zeros,
                              gate.bits, gate.in_features, gate.group_size, split, rho, _ws_arg(workspace, x2))
     else:
@@ -319,7 +326,7 @@ def fused_qkv(x: torch.Tensor, q: PackedLinearWeight, k: PackedLinearWeight, v: 
         sin2 = sin.expand(*lead, head_dim).reshape(rows, head_dim)
     if rows <= decode_threshold:
         total = virtual_rows("qkv", q.out_features, k.out_features, v.out_features)
-        split = _resolve(split_k, rho, rows, total, q.in_features, x2.device)
+        split = _resolve(split_k, rho, rows, total, q.in_features, x2.device, x2.dtype, q.group_size)
         if rope is None:
             rc, rs, hd = _none_like(x2), _none_like(x2), 0
         else:

@@ -208,7 +208,7 @@ class DecodeStack:
             self._o_local = torch.empty(B, dl, dtype=torch.float16, device=self.device)
             self._m_local = torch.empty(B, fl, dtype=torch.float16, device=self.device)
         none = torch.empty(0, dtype=torch.float16, device=self.device)
-        sk = lambda rows, k: _resolve(None, 1, B, rows, k, self.device)
+        sk = lambda rows, k: _resolve(None, 1, B, rows, k, self.device, torch.float16, self.blocks[0].o.group_size)
         xq, xa, xm, xy = self._buf("q", B, d), self._buf("a", B, d), self._buf("m", B, f), self._buf("y", B, d)
         for blk in self.blocks:
             w = blk.qkv
