@@ -186,7 +186,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     const uint32_t tmem_full = s_bar + 8u * (3 * kStages), tmem_empty = s_bar + 8u * (3 * kStages + 1);
     auto full_p = [&](int s) { return s_bar + 8u * (3 * kStages + 2 + s); };
     auto empty_p = [&](int s) { return s_bar + 8u * (3 * kStages + 2 + kPackedSlots + s); };
-    constexpr uint32_t kNumBars = 3 * kStages + 2 + 2 * kPackedSlots;
+    const uint32_t final_full = s_bar + 8u * (3 * kStages + 2 + 2 * kPackedSlots);   // the CTA's last accumulator is complete
+    constexpr uint32_t kNumBars = 3 * kStages + 3 + 2 * kPackedSlots;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kBarOff + 8 * kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kBarOff + 8 * kNumBars + 8);
 
@@ -199,6 +200,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         }
         mbar_init(tmem_full, 1);
         mbar_init(tmem_empty, 4);
+        mbar_init(final_full, 1);
         for (int s = 0; s < kPackedSlots; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kDequantWarps); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -215,6 +217,39 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     const int ntiles = P.tiles_m * P.tiles_n;
     const int nsuper = (P.kblocks + 1) >> 1;                         // packed super-blocks per tile
     int gave_up = 0;
+
+    // Accumulator chunks (32 token columns each) cbegin, cbegin + cstep, ... of `tile` -> bias, activation, fp16, global.
+    // Lane = weight row of this warp's TMEM lane quadrant, so the 32 lanes of a store are 64 contiguous bytes of
+    // one token's output row.
+    auto drain = [&](int tile, int cbegin, int cstep) {
+        const int q = warp & 3;
+        const int m0 = (tile % P.tiles_m) * kBT;
+        const int n = (tile / P.tiles_m) * kBN + q * 32 + lane;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+        const bool nlive = n < P.N;
+        const float bias = (nlive && P.bias != nullptr) ? __half2float(P.bias[n]) : 0.f;
+#pragma unroll 1
+        for (int c0 = 32 * cbegin; c0 < kBT; c0 += 32 * cstep) {
+            uint32_t v[32];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                         "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                           "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                         : "r"(taddr + (uint32_t)c0));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (nlive) {
+                __half* ocol = P.out + (size_t)(m0 + c0) * P.N + n;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (m0 + c0 + j < P.M)
+                        ocol[(size_t)j * P.N] = __float2half_rn(activate(__uint_as_float(v[j]) + bias, P.act));
+                }
+            }
+        }
+    };
 
 #ifdef CB_WS_BARE
     const bool bare = true;      // diagnostic build: only the MMA issuer and the epilogue run
@@ -296,6 +331,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 }
                 if (gave_up) break;
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tmem_full) : "memory");
+                if (tile + (int)gridDim.x >= ntiles)     // also wakes the dequantiser warps, which help drain the last tile
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(final_full) : "memory");
             }
         }
     } else if (warp < kFirstEpiWarp) {
@@ -407,39 +444,24 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             __syncwarp();
             if (lane == 0) { mbar_arrive(full_w(s)); mbar_arrive(empty_p(slot)); }
         }
+        // All stages are expanded: help the epilogue warps drain the CTA's last accumulator (workers 1..4 of five
+        // per lane quadrant).  A barrier of its own, completed once, tells these warps that it is ready.
+        if (my_tiles > 0 && !gave_up) {
+            if (!__all_sync(0xffffffffu, mbar_wait(final_full, 0, abort_flag))) gave_up = 3;
+            else {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                drain((int)blockIdx.x + (my_tiles - 1) * (int)gridDim.x, grp + 1, 5);
+            }
+        }
     } else if (warp < kPackedWarp) {
-        // ================= epilogue: TMEM -> registers -> global (lane = weight row, column = token) =================
-        const int q = warp & 3;                                       // the TMEM lane quadrant this warp may read
+        // ================= epilogue warps: drain every accumulator; on the CTA's last tile the dequantisers help =================
         int tcount = 0;
         for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x, ++tcount) {
-            const int m0 = (tile % P.tiles_m) * kBT;
-            const int n = (tile / P.tiles_m) * kBN + q * 32 + lane;
             if (!__all_sync(0xffffffffu, mbar_wait(tmem_full, tcount & 1, abort_flag))) { gave_up = 4; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-            const bool nlive = n < P.N;
-            const float bias = (nlive && P.bias != nullptr) ? __half2float(P.bias[n]) : 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < kBT; c0 += 32) {
-                uint32_t v[32];
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                               "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                               "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                               "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                             : "r"(taddr + (uint32_t)c0));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (nlive) {
-                    __half* ocol = P.out + (size_t)(m0 + c0) * P.N + n;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (m0 + c0 + j < P.M)
-                            ocol[(size_t)j * P.N] = __float2half_rn(activate(__uint_as_float(v[j]) + bias, P.act));
-                    }
-                }
-            }
+            const bool last = tile + (int)gridDim.x >= ntiles;
+            if (last) drain(tile, 0, 5);            // worker 0 of five per lane quadrant
+            else drain(tile, 0, 1);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty);
