@@ -314,6 +314,32 @@ def test_prefill_gemm_tensor_core_kernel(bits, M, n, k):
     assert _C.decode_status() == 0
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("M,n,k,gs", [(129, 8, 128, 128), (257, 136, 256, 64), (513, 2048, 384, 128), (700, 264, 896, 64),
+                                      (2049, 1032, 1152, 128)])
+def test_prefill_gemm_edge_shapes_of_the_weight_stationary_kernel(bits, M, n, k, gs):
+    """Just above 128 tokens, ragged token and weight-row tiles, two to eighteen pipeline stages (the rings wrap at
+    six stages and four packed slots), group 64 (a scale change inside a packed super-block), several tiles per
+    CTA at M = 2049: the weights-in-TMEM kernel against the rounded-weight product and against the CUDA-core kernel."""
+    from crispybits_kernels import _C, packed_linear
+    w, wd, bd = cached(n, k, bits, torch.float16, True, 11, gs, 0.02)
+    x = torch.randn(M, k, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(M + k))
+    _C.set_option(3, 2)
+    try:
+        y = packed_linear(x, w, act="relu", decode_threshold=0)
+    finally:
+        _C.set_option(3, 0)
+    rounded = torch.relu(x.float() @ wd.half().float().T + bd)
+    assert rel_err(y, rounded) < 1e-3
+    _C.set_option(1, 1)
+    try:
+        slow = packed_linear(x, w, act="relu", decode_threshold=0)
+    finally:
+        _C.set_option(1, 0)
+    assert rel_err(y, slow.float()) < 1e-3
+    assert _C.decode_status() == 0
+
+
 @pytest.mark.parametrize("M,n,k", [(300, 4096, 4096), (1024, 1000, 11008)])
 def test_prefill_gemm_is_stable_over_repeated_launches(M, n, k):
     """Shapes with fewer tiles than SMs, where the kernel's roles run at other relative speeds than in the large
