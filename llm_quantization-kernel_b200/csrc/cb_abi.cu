@@ -383,7 +383,8 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out, int6
     if (use_tensor_cores && !g_force_generic) {
         // tcgen05 kernels when the problem is inside their domain (-1 = it is not): above 128 tokens the one that
         // keeps the expanded weights in tensor memory and serves 256 tokens per expansion, else the 128-token one
-        if (g_gemm_kernel == 2 || (g_gemm_kernel == 0 && M > 128)) {
+        const bool ws_first = g_gemm_kernel == 2 || (g_gemm_kernel == 0 && (M > 128 || dtype == CB_BF16));
+        if (ws_first) {
             const int rc3 = launch_gemm_ws(dtype, x, M, w, out, K, bits, group_size, act, reinterpret_cast<cudaStream_t>(stream));
             if (rc3 != -1) return rc3;
         }

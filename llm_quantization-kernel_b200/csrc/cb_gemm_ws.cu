@@ -43,7 +43,9 @@ constexpr uint32_t kPackedSlotBytes = kBN * 64;     // 128 rows x 128 codes at 4
 constexpr uint32_t kSmemBytes = kStages * kXBytes + kPackedSlots * kPackedSlotBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kAccCols = 256, kAStageCols = 32;
 constexpr long long kWaitCycles = 2000000000ll;     // about a second at boost clock
-constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kBT >> 3) << 17) | ((uint32_t)(kBN >> 4) << 24);   // f16 x f16 -> f32, K-major A and B
+// instruction descriptor: fp32 accumulator, A and B both fp16 (format 0) or both bf16 (format 1), K-major, N = 256, M = 128
+constexpr uint32_t kIdescF16 = (1u << 4) | ((uint32_t)(kBT >> 3) << 17) | ((uint32_t)(kBN >> 4) << 24);
+constexpr uint32_t kIdescBF16 = kIdescF16 | (1u << 7) | (1u << 10);
 
 __device__ int g_gemm_ws_status;   // 0 = ok, else the role that gave up waiting (1 x producer, 2 mma, 3 dequant, 4 epilogue, 5 packed producer)
 
@@ -167,7 +169,86 @@ template <> struct Dequant16<3> {
     }
 };
 
-template <int BITS>
+// ---- the same for bfloat16 activations: the expanded weight is round_bf16((q - zero) * scale) -------------------------
+// bf16 has seven mantissa bits, so a field is only exact at bits 0..6 of its half: (field | 0x4300) reads as
+// 128 + code * 2^p for p <= 4.  A multiply by 2^a + 1 first copies the byte's upper codes into the upper half.
+__device__ __forceinline__ uint32_t b2fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t b2mul(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t b2sub(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+constexpr uint32_t kMagicB = 0x43004300u;      // bf16x2(128, 128)
+constexpr uint32_t kOneB = 0x3F803F80u;        // bf16x2(1, 1)
+
+template <int BITS> struct Dequant16B;
+
+template <> struct Dequant16B<4> {
+    __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t zz, uint32_t ss, uint32_t (&t)[8]) {
+        const uint32_t add = b2sub(0xC300C300u, zz);                 // -(128 + z), exact: 128 + 15 needs eight bits
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = __byte_perm(w[j >> 2], 0u, 0x4440 | (j & 3)) * 0x1001u;   // byte j: its low code at bits 0-3 of the low half, its high code at bits 0-3 of the high half
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = lop3_and_or(t[j], 0x000F000Fu, kMagicB);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = b2fma(t[j], kOneB, add);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = b2mul(t[j], ss);
+    }
+};
+
+template <> struct Dequant16B<2> {
+    __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t zz, uint32_t ss, uint32_t (&t)[8]) {
+        const uint32_t add0 = b2sub(0xC300C300u, zz);                // -(128 + z)    fields at bit 0
+        const uint32_t add4 = b2sub(0xC100C100u, zz);                // -(8 + z)      fields at bit 4, scaled by 1/16
+        uint32_t b[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = __byte_perm(w[0], 0u, 0x4440 | j) * 0x4001u;   // low half: code 4j at bits 0-1, 4j+2 at bits 4-5; high half: 4j+1 at bits 0-1, 4j+3 at bits 4-5
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            t[2 * j] = lop3_and_or(b[j], 0x00030003u, kMagicB);      // codes 4j, 4j+1
+            t[2 * j + 1] = lop3_and_or(b[j], 0x00300030u, kMagicB);  // codes 4j+2, 4j+3 (as 128 + 16 * code)
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            t[2 * j] = b2fma(t[2 * j], kOneB, add0);
+            t[2 * j + 1] = b2fma(t[2 * j + 1], 0x3D803D80u, add4);   // * 1/16
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = b2mul(t[j], ss);
+    }
+};
+
+template <> struct Dequant16B<3> {
+    __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t zz, uint32_t ss, uint32_t (&t)[8]) {
+        const uint32_t add = b2sub(0xC300C300u, zz);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int pos = 6 * j, wi = pos >> 5, off = pos & 31;
+            if (off + 6 <= 32) t[j] = w[wi] >> off;
+            else t[j] = __funnelshift_r(w[0], w[1], off);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = (t[j] & 0x3Fu) * 0x2001u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = lop3_and_or(t[j], 0x00070007u, kMagicB);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = b2fma(t[j], kOneB, add);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = b2mul(t[j], ss);
+    }
+};
+
+template <int BITS, bool BF>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const GemmParams P) {
     extern __shared__ unsigned char smem_raw[];
@@ -227,7 +308,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         const int n = (tile / P.tiles_m) * kBN + q * 32 + lane;
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
         const bool nlive = n < P.N;
-        const float bias = (nlive && P.bias != nullptr) ? __half2float(P.bias[n]) : 0.f;
+        float bias = 0.f;
+        if (nlive && P.bias != nullptr)
+            bias = BF ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.bias)[n]) : __half2float(P.bias[n]);
 #pragma unroll 1
         for (int c0 = 32 * cbegin; c0 < kBT; c0 += 32 * cstep) {
             uint32_t v[32];
@@ -244,8 +327,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 __half* ocol = P.out + (size_t)(m0 + c0) * P.N + n;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    if (m0 + c0 + j < P.M)
-                        ocol[(size_t)j * P.N] = __float2half_rn(activate(__uint_as_float(v[j]) + bias, P.act));
+                    if (m0 + c0 + j < P.M) {
+                        const float y = activate(__uint_as_float(v[j]) + bias, P.act);
+                        if constexpr (BF) reinterpret_cast<__nv_bfloat16*>(ocol)[(size_t)j * P.N] = __float2bfloat16_rn(y);
+                        else ocol[(size_t)j * P.N] = __float2half_rn(y);
+                    }
                 }
             }
         }
@@ -324,7 +410,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                         const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
                         asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                                      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}"
-                                     ::"r"(tmem_base), "r"(a_tmem + (uint32_t)k * 8u), "l"(bdesc), "r"(kIdesc), "r"(accumulate), "r"(0u) : "memory");
+                                     ::"r"(tmem_base), "r"(a_tmem + (uint32_t)k * 8u), "l"(bdesc), "r"(BF ? kIdescBF16 : kIdescF16), "r"(accumulate), "r"(0u) : "memory");
                     }
                     // the stage (shared-memory x tile and TMEM weight columns) may be refilled once these MMAs have read it
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(empty(s)) : "memory");
@@ -423,7 +509,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 8; ++j) t8[j] = w2[j & 1] ^ zz ^ ss;      // diagnostic: no unpack arithmetic
 #else
-                Dequant16<BITS>::run(w2, zz, ss, t8);
+                if constexpr (BF) Dequant16B<BITS>::run(w2, zz, ss, t8);
+                else Dequant16<BITS>::run(w2, zz, ss, t8);
 #endif
 #pragma unroll
                 for (int j = 0; j < 8; ++j) t[8 * kq + j] = t8[j];
@@ -497,16 +584,16 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int BITS>
+template <int BITS, bool BF>
 int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const GemmParams& P, int grid, cudaStream_t stream) {
     static bool attr_done[64] = {};
     int dev = 0;
     CB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        CB_CUDA_TRY(cudaFuncSetAttribute(gemm_ws_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        CB_CUDA_TRY(cudaFuncSetAttribute(gemm_ws_kernel<BITS, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    gemm_ws_kernel<BITS><<<grid, kThreads, kSmemBytes, stream>>>(xmap, wmap, P);
+    gemm_ws_kernel<BITS, BF><<<grid, kThreads, kSmemBytes, stream>>>(xmap, wmap, P);
     CB_CUDA_TRY(cudaGetLastError());
     return CB_OK;
 }
@@ -514,11 +601,11 @@ int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const GemmParams&
 }  // namespace
 
 // CB_OK after launching; a CB_ERR_* code on a CUDA error; -1 when the problem is outside this kernel's
-// domain (fp16, K a multiple of 128, group size a multiple of 64, N a multiple of 8, 16-byte aligned
+// domain (fp16 or bf16, K a multiple of 128, group size a multiple of 64, N a multiple of 8, 16-byte aligned
 // x / packed / out) and the caller should use another kernel.
 int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
                    int64_t gs, int act, cudaStream_t stream) {
-    if (dtype != CB_F16 || K % 128 != 0 || gs % kBK != 0 || w->n % 8 != 0 || M < 1) return -1;
+    if ((dtype != CB_F16 && dtype != CB_BF16) || K % 128 != 0 || gs % kBK != 0 || w->n % 8 != 0 || M < 1) return -1;
     if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(w->packed) % 16 ||
         reinterpret_cast<uintptr_t>(out) % 16)
         return -1;
@@ -534,7 +621,7 @@ int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void
         const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
         const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
         const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBT};
-        const CUresult cr = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+        const CUresult cr = enc(&xmap, dtype == CB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) { set_error("packed_gemm: cuTensorMapEncodeTiled(x) failed (%d)", (int)cr); return CB_ERR_CUDA; }
@@ -560,9 +647,9 @@ int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void
     P.tiles_m = (int)((M + kBT - 1) / kBT); P.tiles_n = (int)((w->n + kBN - 1) / kBN); P.kblocks = (int)(K / kBK);
     const int grid = std::min(sms, P.tiles_m * P.tiles_n);
     switch (bits) {
-        case 2: return launch_t<2>(xmap, wmap, P, grid, stream);
-        case 3: return launch_t<3>(xmap, wmap, P, grid, stream);
-        default: return launch_t<4>(xmap, wmap, P, grid, stream);
+        case 2: return dtype == CB_BF16 ? launch_t<2, true>(xmap, wmap, P, grid, stream) : launch_t<2, false>(xmap, wmap, P, grid, stream);
+        case 3: return dtype == CB_BF16 ? launch_t<3, true>(xmap, wmap, P, grid, stream) : launch_t<3, false>(xmap, wmap, P, grid, stream);
+        default: return dtype == CB_BF16 ? launch_t<4, true>(xmap, wmap, P, grid, stream) : launch_t<4, false>(xmap, wmap, P, grid, stream);
     }
 }
 

@@ -340,6 +340,28 @@ def test_prefill_gemm_edge_shapes_of_the_weight_stationary_kernel(bits, M, n, k,
     assert _C.decode_status() == 0
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("M,n,k,gs", [(5, 264, 256, 128), (130, 520, 1024, 64), (300, 4096, 4096, 128), (1024, 1000, 11008, 128)])
+def test_prefill_gemm_bf16_tensor_core_kernel(bits, M, n, k, gs):
+    """bfloat16 through the weights-in-TMEM kernel: the expanded weight is round_bf16((q - zero) * scale) as in the
+    reference's tensor-core path (packed_gemm.cu:56,60), fp32 accumulation, bf16 output."""
+    from crispybits_kernels import _C, packed_linear
+    w, wd, bd = cached(n, k, bits, torch.bfloat16, True, 13, gs, 0.02)
+    x = torch.randn(M, k, device=DEV, dtype=torch.bfloat16, generator=torch.Generator(DEV).manual_seed(M))
+    y = packed_linear(x, w, act="silu", decode_threshold=0)
+    assert y.dtype == torch.bfloat16
+    rounded = torch.nn.functional.silu(x.float() @ wd.bfloat16().float().T + bd)
+    assert rel_err(y, rounded) < 8e-3                        # one bf16 output rounding
+    close(y, ref_linear(x, wd, bd, "silu"), torch.bfloat16)   # the reference's bf16 bound against fp32 weights
+    _C.set_option(1, 1)
+    try:
+        slow = packed_linear(x, w, act="silu", decode_threshold=0)     # CUDA-core kernel, same rounded-weight numerics
+    finally:
+        _C.set_option(1, 0)
+    assert rel_err(y, slow.float()) < 8e-3
+    assert _C.decode_status() == 0
+
+
 @pytest.mark.parametrize("M,n,k", [(300, 4096, 4096), (1024, 1000, 11008)])
 def test_prefill_gemm_is_stable_over_repeated_launches(M, n, k):
     """Shapes with fewer tiles than SMs, where the kernel's roles run at other relative speeds than in the large
