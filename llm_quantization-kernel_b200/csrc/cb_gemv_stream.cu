@@ -119,9 +119,12 @@ template <int BITS> __device__ __forceinline__ void lds_chunk(const unsigned cha
     }
 }
 
-template <int BITS>
+template <int BITS, bool BF>
 __global__ void __launch_bounds__(kThreads, 2)
 gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
+    // BF: activations, scales, zeros and outputs are bfloat16 (the pointer types below only stand for "16-bit elements")
+    using U = std::conditional_t<BF, UnpackB<BITS>, Unpack<BITS>>;
+    using OutT = std::conditional_t<BF, __nv_bfloat16, __half>;
     extern __shared__ __align__(128) unsigned char smem[];
     // The next kernel of the stream may start right away: it only prefetches its own weights until
     // this grid has completed.
@@ -245,7 +248,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
             uint32_t xf[16];
 #pragma unroll
             for (int m = 0; m < 16; ++m) {
-                const int lo = Unpack<BITS>::pair_lo(m), hi = lo + Unpack<BITS>::pair_gap();
+                const int lo = U::pair_lo(m), hi = lo + U::pair_gap();
                 xf[m] = __byte_perm(xnext[lo >> 1], xnext[hi >> 1], (lo & 1) ? 0x7632 : 0x5410);
             }
             if (!CB_DBG(8)) load_x(gl + 1 < wg_end ? gl + 1 : wg_begin, xnext);      // wraps to the first group for the next pass
@@ -259,12 +262,12 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
                     const __half* z1 = z0 + 4 * S.meta_stride;
                     // rows past the end of the slab were never copied: give them scale 0 and a finite zero point
                     const bool ok0 = row0 + tile * 16 + g < row_end, ok1 = row0 + tile * 16 + g + 8 < row_end;
-                    const float cs0 = ok0 ? __half2float(s0[gl]) : 0.f, cs1 = ok1 ? __half2float(s1[gl]) : 0.f;
+                    const float cs0 = ok0 ? to_f32(reinterpret_cast<const OutT*>(s0)[gl]) : 0.f, cs1 = ok1 ? to_f32(reinterpret_cast<const OutT*>(s1)[gl]) : 0.f;
                     const uint32_t zr0 = ok0 ? (uint32_t)reinterpret_cast<const unsigned short*>(z0)[gl] : 0u;
                     const uint32_t zr1 = ok1 ? (uint32_t)reinterpret_cast<const unsigned short*>(z1)[gl] : 0u;
-                    uint32_t ka[Unpack<BITS>::kConsts], kb[Unpack<BITS>::kConsts];
-                    Unpack<BITS>::consts(zr0 | (zr0 << 16), ka);
-                    Unpack<BITS>::consts(zr1 | (zr1 << 16), kb);
+                    uint32_t ka[U::kConsts], kb[U::kConsts];
+                    U::consts(zr0 | (zr0 << 16), ka);
+                    U::consts(zr1 | (zr1 << 16), kb);
                     uint32_t wa[BITS], wb[BITS], ea[16], eb[16];
                     lds_chunk<BITS>(arow, wa);
                     lds_chunk<BITS>(arow + 8 * (size_t)S.pitch, wb);
@@ -272,8 +275,8 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) { ea[i] = wa[i % BITS] + ka[0]; eb[i] = wb[i % BITS] + kb[0]; }
                     } else {
-                    Unpack<BITS>::run(wa, ka, ea);
-                    Unpack<BITS>::run(wb, kb, eb);
+                    U::run(wa, ka, ea);
+                    U::run(wb, kb, eb);
                     }
                     // Four independent accumulation chains of depth two: on this GPU a dependent mma.sync
                     // issues ~110 cycles after its predecessor, so the eight k-steps must not form one chain.
@@ -285,14 +288,19 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
 #pragma unroll
                         for (int j = 0; j < 4; ++j) { d0[j] = __uint_as_float(h & 0x3fffffff); d1[j] = d2[j] = d3[j] = 0.f; }
                     } else {
-                    mma16816(d0, ea[0], eb[0], ea[1], eb[1], xf[0], xf[1], zero4);
-                    mma16816(d1, ea[2], eb[2], ea[3], eb[3], xf[2], xf[3], zero4);
-                    mma16816(d2, ea[4], eb[4], ea[5], eb[5], xf[4], xf[5], zero4);
-                    mma16816(d3, ea[6], eb[6], ea[7], eb[7], xf[6], xf[7], zero4);
-                    mma16816(d0, ea[8], eb[8], ea[9], eb[9], xf[8], xf[9], d0);
-                    mma16816(d1, ea[10], eb[10], ea[11], eb[11], xf[10], xf[11], d1);
-                    mma16816(d2, ea[12], eb[12], ea[13], eb[13], xf[12], xf[13], d2);
-                    mma16816(d3, ea[14], eb[14], ea[15], eb[15], xf[14], xf[15], d3);
+                    auto mma = [](float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
+                                  const float (&c)[4]) {
+                        if constexpr (BF) mma16816_bf16(d, a0, a1, a2, a3, b0, b1, c);
+                        else mma16816(d, a0, a1, a2, a3, b0, b1, c);
+                    };
+                    mma(d0, ea[0], eb[0], ea[1], eb[1], xf[0], xf[1], zero4);
+                    mma(d1, ea[2], eb[2], ea[3], eb[3], xf[2], xf[3], zero4);
+                    mma(d2, ea[4], eb[4], ea[5], eb[5], xf[4], xf[5], zero4);
+                    mma(d3, ea[6], eb[6], ea[7], eb[7], xf[6], xf[7], zero4);
+                    mma(d0, ea[8], eb[8], ea[9], eb[9], xf[8], xf[9], d0);
+                    mma(d1, ea[10], eb[10], ea[11], eb[11], xf[10], xf[11], d1);
+                    mma(d2, ea[12], eb[12], ea[13], eb[13], xf[12], xf[13], d2);
+                    mma(d3, ea[14], eb[14], ea[15], eb[15], xf[14], xf[15], d3);
                     }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) { d0[j] = (d0[j] + d1[j]) + (d2[j] + d3[j]); d1[j] = 0.f; }
@@ -329,7 +337,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
                 partner += myred[((w * 2 + tile) * 32 + pl) * 4 + fe];
             }
             if (tile < ntile && v < row_end && b < P.B && !failed) {
-                if (P.split_k == 1) epilogue<__half>(P, b, v, mine, partner);
+                if (P.split_k == 1) epilogue<OutT>(P, b, v, mine, partner);
                 else P.partial[((size_t)split * P.B + b) * P.V + v] = mine;
             }
         }
@@ -357,7 +365,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
                     m += __ldcg(ps + v);
                     if (has_partner) pt += __ldcg(ps + (v ^ 1));
                 }
-                epilogue<__half>(P, b, v, m, pt);
+                epilogue<OutT>(P, b, v, m, pt);
             }
             if (tid == 0) P.counters[slab] = 0;
         }
@@ -365,7 +373,7 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
     peer_signal(P, peer_epoch);
 }
 
-template <int BITS>
+template <int BITS, bool BF>
 int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, size_t scratch_bytes,
              cudaStream_t stream) {
     const int sms = sm_count_current();
@@ -459,7 +467,7 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
     S.grp_q = gpairs / split; S.grp_r = gpairs % split;
 
     static bool attr_done[64] = {};     // per device: the opt-in to large dynamic shared memory
-    auto kern = gemv_stream_kernel<BITS>;
+    auto kern = gemv_stream_kernel<BITS, BF>;
     int dev = 0;
     CB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
@@ -489,15 +497,18 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
 // the kernel's domain (the caller then uses the generic kernel).
 int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, int64_t rho, bool pdl,
                        void* scratch, size_t scratch_bytes, cudaStream_t stream) {
-    if (dtype != CB_F16 || P.group_size != 128 || P.K % 256 != 0 || P.B > kMaxBatchBlock || P.B < 1) return -1;
+    if ((dtype != CB_F16 && dtype != CB_BF16) || P.group_size != 128 || P.K % 256 != 0 || P.B > kMaxBatchBlock || P.B < 1) return -1;
     if (reinterpret_cast<uintptr_t>(x) % 16 != 0) return -1;
     for (int i = 0; i < 3; ++i)
         if (reinterpret_cast<uintptr_t>(P.p[i].w) % 16 != 0) return -1;
     if ((P.mode != CB_MODE_GEMV) && (P.V & 1)) return -1;
     switch (bits) {
-        case 2: return launch_t<2>(x, P, rho, pdl, scratch, scratch_bytes, stream);
-        case 3: return launch_t<3>(x, P, rho, pdl, scratch, scratch_bytes, stream);
-        default: return launch_t<4>(x, P, rho, pdl, scratch, scratch_bytes, stream);
+        case 2: return dtype == CB_BF16 ? launch_t<2, true>(x, P, rho, pdl, scratch, scratch_bytes, stream)
+                                        : launch_t<2, false>(x, P, rho, pdl, scratch, scratch_bytes, stream);
+        case 3: return dtype == CB_BF16 ? launch_t<3, true>(x, P, rho, pdl, scratch, scratch_bytes, stream)
+                                        : launch_t<3, false>(x, P, rho, pdl, scratch, scratch_bytes, stream);
+        default: return dtype == CB_BF16 ? launch_t<4, true>(x, P, rho, pdl, scratch, scratch_bytes, stream)
+                                         : launch_t<4, false>(x, P, rho, pdl, scratch, scratch_bytes, stream);
     }
 }
 

@@ -247,6 +247,45 @@ def test_streamlined_kernel_agrees_with_generic_kernel(bits, mode):
 
 
 @pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("mode", ["gemv", "gate_up", "qkv_rope"])
+def test_bf16_ring_kernel_agrees_with_generic_kernel(bits, mode):
+    """bfloat16 decode through the ring kernel (bf16 MMA, 0x4300 magic-number unpack) against the generic fp32-FMA
+    kernel on the same call and against the fp32 dequantise-then-matmul."""
+    from crispybits_kernels import _C, fused_gate_up, fused_qkv, packed_linear, permute_for_rope
+    K = 2048
+    x = torch.randn(3, K, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        if mode == "gemv":
+            w, _, _ = cached(1000, K, bits, torch.bfloat16, True, 4)
+            return [packed_linear(x, w, sk, 1, "silu") for sk in (1, 3)]
+        if mode == "gate_up":
+            g_, _, _ = cached(1376, K, bits, torch.bfloat16, False, 1)
+            u_, _, _ = cached(1376, K, bits, torch.bfloat16, False, 2)
+            return [fused_gate_up(x, g_, u_, sk, 1) for sk in (1, 2)]
+        q, _, _ = cached(1024, K, bits, torch.bfloat16, True, 1)
+        k, _, _ = cached(256, K, bits, torch.bfloat16, True, 2)
+        v, _, _ = cached(256, K, bits, torch.bfloat16, False, 3)
+        q, k = permute_for_rope(q, 128), permute_for_rope(k, 128)
+        cos, sin = rope_tables(3, 128, DEV)
+        return [o for sk in (1, 4) for o in fused_qkv(x, q, k, v, sk, 1, rope=(cos, sin, 128))]
+
+    fast = run()
+    _C.set_option(1, 1)
+    try:
+        slow = run()
+    finally:
+        _C.set_option(1, 0)
+    for a, b in zip(fast, slow):
+        assert a.dtype == torch.bfloat16
+        assert rel_err(a, b.float()) < 8e-3          # two bf16 output roundings apart at most
+    if mode == "gemv":
+        w, wd, bd = cached(1000, K, bits, torch.bfloat16, True, 4)
+        close(fast[0], ref_linear(x, wd, bd, "silu"), torch.bfloat16)
+    assert _C.decode_status() == 0
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
 @pytest.mark.parametrize("B", [1, 5, 8])
 def test_register_streaming_kernel_full_size(bits, B):
     """The register-streaming decode kernel forced on (option 2 = 2): ragged last tile, several tiles per CTA,
