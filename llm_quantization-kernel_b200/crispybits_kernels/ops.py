@@ -230,11 +230,11 @@ def _resolve(split_k: Optional[int], rho: int, batch: int, v_rows: int, k: int, 
     nchunks = ceil(k / 32)
     if split_k is not None:
         return max(1, min(int(split_k), nchunks))
-    # Inside the domain of the fp16 ring kernel (group 128, K a multiple of 256, up to 8 batch rows) no split is
+    # Inside the domain of the fp16 / bf16 ring kernel (group 128, K a multiple of 256, up to 8 batch rows) no split is
     # the measured optimum on B200 at every shape tried, also for 512- and 1376-row shards (3.2 us against 5.0 us
     # with the underfill rule's split): the kernel spreads a matrix over the SMs by rows and a K split costs it
     # a partial-sum round trip through memory that is as long as the whole launch.
-    if dtype == torch.float16 and group_size == 128 and k % 256 == 0 and batch <= BATCH_BLOCK:
+    if dtype in (torch.float16, torch.bfloat16) and group_size == 128 and k % 256 == 0 and batch <= BATCH_BLOCK:
         return 1
     if device.type == "cuda":
         index = device.index if device.index is not None else torch.cuda.current_device()
