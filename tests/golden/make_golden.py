@@ -3,7 +3,7 @@
 
 Run on a machine that holds the reference tree (it is imported, never copied):
 
-    python tests/golden/make_golden.py [path/to/reference/Crispybits/Kernel]
+    python tests/golden/make_golden.py path/to/reference/Crispybits/Kernel
 
 The script imports the reference's ``crispybits_kernels.reference`` (quantizer,
 bitstream) and ``crispybits_kernels.emulator`` (decode / prefill arithmetic),
@@ -18,7 +18,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/Crispybits/Kernel"
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py <path to the reference's Crispybits/Kernel directory>")
+REF = sys.argv[1]
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
 from crispybits_kernels import emulator as E  # noqa: E402
