@@ -152,6 +152,13 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out,
                    int64_t K, int bits, int64_t group_size, int dtype,
                    int act, int use_tensor_cores, void* stream);
 
+/* Fused prefill gate/up  out[M,n] = silu(x Wg^T) * (x Wu^T)  in one tcgen05 launch (gate and up rows share a
+ * tile as neighbouring tensor-memory lanes).  The reference runs two GEMMs and an elementwise product here
+ * (Crispybits/Kernel/crispybits_kernels/ops.py:216-220).  Returns CB_ERR_UNSUPPORTED outside the kernel's domain
+ * (fp16 / bf16, K a multiple of 128, group size a multiple of 64); the caller then uses cb_packed_gemm twice. */
+int cb_fused_gate_up_gemm(const void* x, int64_t M, const cb_weight* gate, const cb_weight* up, void* out,
+                          int64_t K, int bits, int64_t group_size, int dtype, void* stream);
+
 /* Bit-exact unpack  codes[n,K] (int32) <- packed[n, ceil(K/32)*bits]; the device counterpart of
  * unpack_codes (Crispybits/Kernel/crispybits_kernels/reference.py:58-67; csrc/bitpack.cuh:10-18),
  * exported so that the integer layout can be checked bit-for-bit against the oracle. */

@@ -399,6 +399,35 @@ def unpack_codes(packed: torch.Tensor, bits: int, in_features: int) -> torch.Ten
     return out
 
 
+_lib.cb_fused_gate_up_gemm.argtypes = [_vp, _i64, _WP, _WP, _vp, _i64, _int, _i64, _int, _vp]
+_lib.cb_fused_gate_up_gemm.restype = _int
+
+
+def fused_gate_up_gemm(x, wg, sg, zg, wu, su, zu, bits, in_features, group_size):
+    """silu(x Wg^T) * (x Wu^T) for a prefill batch in one launch, or None when the shape is outside the fused
+    kernel's domain (the caller then runs two GEMMs and a product, as the reference does)."""
+    bits, k, gs = int(bits), int(in_features), int(group_size)
+    _check_x(x, k)
+    _check_weight(x, wg, sg, zg, bits, k, gs, "fused_gate_up_gemm(gate)")
+    _check_weight(x, wu, su, zu, bits, k, gs, "fused_gate_up_gemm(up)")
+    if wg.shape != wu.shape:
+        _fail("gate/up packed shapes must match")
+    if x.dtype not in (torch.float16, torch.bfloat16) or k % 128 or gs % 64:
+        return None
+    M, n = x.shape[0], wg.shape[0]
+    out = torch.empty((M, n), dtype=x.dtype, device=x.device)
+    if M == 0:
+        return out
+    with torch.cuda.device(x.device):
+        g, u = _weight(wg, sg, zg, None), _weight(wu, su, zu, None)
+        rc = _lib.cb_fused_gate_up_gemm(x.data_ptr(), M, ctypes.byref(g), ctypes.byref(u), out.data_ptr(), k, bits, gs,
+                                        _DTYPE[x.dtype], _stream(x))
+    if rc == 3:          # CB_ERR_UNSUPPORTED
+        return None
+    _rc(rc)
+    return out
+
+
 _lib.cb_quantize_pack.argtypes = [_vp, _int, _i64, _i64, _int, _i64, _vp, _vp, _vp, _int, _vp]
 _lib.cb_quantize_pack.restype = _int
 

@@ -280,7 +280,8 @@ def packed_linear(x: torch.Tensor, w: PackedLinearWeight, split_k: Optional[int]
 def fused_gate_up(x: torch.Tensor, gate: PackedLinearWeight, up: PackedLinearWeight,
                   split_k: Optional[int] = None, rho: int = 1, decode_threshold: int = DECODE_THRESHOLD,
                   workspace: Optional[torch.Tensor] = None):
-    """silu(x Wg^T) * (x Wu^T) in one decode launch; two prefill GEMMs and a product above the threshold."""
+    """silu(x Wg^T) * (x Wu^T): one decode launch up to the threshold, above it one fused tcgen05 prefill launch
+    (two prefill GEMMs and a product where that kernel does not apply)."""
     _check_ext()
     if gate.bits != up.bits:
         raise ValueError("fused Gate/Up requires the same precision for Gate and Up within a block")
@@ -291,12 +292,19 @@ def fused_gate_up(x: torch.Tensor, gate: PackedLinearWeight, up: PackedLinearWei
         y = _C.fused_gate_up(x2, gate.packed, gate.scales, gate.zeros, up.packed, up.scales, up.zeros,
                              gate.bits, gate.in_features, gate.group_size, split, rho, _ws_arg(workspace, x2))
     else:
-        none = _none_like(x2)
-        g = _C.packed_gemm(x2, gate.packed, gate.scales, gate.zeros, none, gate.bits, gate.in_features,
-                           gate.group_size, ACT["silu"], True)
-        u = _C.packed_gemm(x2, up.packed, up.scales, up.zeros, none, up.bits, up.in_features,
-                           up.group_size, ACT["none"], True)
-        y = g * u
+        # one fused tcgen05 launch where the backend has it and the shape allows it; else two GEMMs and a product
+        fused = getattr(_C, "fused_gate_up_gemm", None)
+        y = None
+        if fused is not None and gate.group_size == up.group_size and gate.in_features == up.in_features:
+            y = fused(x2, gate.packed, gate.scales, gate.zeros, up.packed, up.scales, up.zeros, gate.bits,
+                      gate.in_features, gate.group_size)
+        if y is None:
+            none = _none_like(x2)
+            g = _C.packed_gemm(x2, gate.packed, gate.scales, gate.zeros, none, gate.bits, gate.in_features,
+                               gate.group_size, ACT["silu"], True)
+            u = _C.packed_gemm(x2, up.packed, up.scales, up.zeros, none, up.bits, up.in_features,
+                               up.group_size, ACT["none"], True)
+            y = g * u
     return y.reshape(*x.shape[:-1], gate.out_features)
 
 

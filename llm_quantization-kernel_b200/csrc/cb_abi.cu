@@ -44,6 +44,8 @@ int launch_peer_wait(const GemvParams& P, cudaStream_t stream);
 int launch_peer_signal(const GemvParams& P, cudaStream_t stream);
 int gemm_status_read_and_clear(int* out);
 int gemm_ws_status_read_and_clear(int* out);
+int launch_gemm_ws_gate_up(int dtype, const void* x, int64_t M, const cb_weight* gate, const cb_weight* up, void* out,
+                           int64_t K, int bits, int64_t gs, cudaStream_t stream);
 int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
                    int64_t gs, int act, cudaStream_t stream);
 int launch_gemm_tc(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
@@ -394,6 +396,23 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out, int6
     const int round_w = (use_tensor_cores && dtype != CB_F32) ? 1 : 0;
     return launch_gemm_simt(dtype, x, M, w, out, K, bits, group_size, act, round_w,
                             reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cb_fused_gate_up_gemm(const void* x, int64_t M, const cb_weight* gate, const cb_weight* up, void* out, int64_t K,
+                          int bits, int64_t group_size, int dtype, void* stream) {
+    int rc = check_common("fused_gate_up_gemm", x, M, K, bits, group_size, dtype);
+    if (rc) return rc;
+    if ((rc = check_weight("fused_gate_up_gemm(gate)", gate, bits))) return rc;
+    if ((rc = check_weight("fused_gate_up_gemm(up)", up, bits))) return rc;
+    CB_REQUIRE(gate->n == up->n, "fused_gate_up_gemm: gate/up shapes must match");
+    if (M == 0) return CB_OK;
+    CB_REQUIRE(out != nullptr, "fused_gate_up_gemm: out is NULL");
+    if (!g_force_generic) {
+        const int rc2 = launch_gemm_ws_gate_up(dtype, x, M, gate, up, out, K, bits, group_size, reinterpret_cast<cudaStream_t>(stream));
+        if (rc2 != -1) return rc2;
+    }
+    set_error("fused_gate_up_gemm: outside the fused kernel's domain (fp16 / bf16, K a multiple of 128, group size a multiple of 64)");
+    return CB_ERR_UNSUPPORTED;
 }
 
 int cb_unpack_codes(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, void* stream) {

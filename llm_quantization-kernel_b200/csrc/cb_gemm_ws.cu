@@ -51,6 +51,7 @@ __device__ int g_gemm_ws_status;   // 0 = ok, else the role that gave up waiting
 
 struct GemmParams {
     const __half* scales; const __half* zeros; const __half* bias; __half* out;
+    const __half* scales2; const __half* zeros2;     // fused gate/up: the up projection's metadata (scales / zeros are the gate's)
     int M, N, K, groups, group_size, act;
     int tiles_m, tiles_n, kblocks;
 };
@@ -248,9 +249,15 @@ template <> struct Dequant16B<3> {
     }
 };
 
-template <int BITS, bool BF>
+// GU: fused gate/up.  The 128 TMEM lanes of a tile are 64 gate rows and the 64 up rows of the same indices,
+// interleaved (lane 2i = gate row n0 + i, lane 2i + 1 = up row n0 + i), so that silu(gate) * up is a product of
+// neighbouring lanes in the epilogue (the virtual-row trick of the decode kernel,
+// Crispybits/Kernel/csrc/packed_gemv.cu:33-42, 61-64); a tile then covers 64 output columns.
+template <int BITS, bool BF, bool GU>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const GemmParams P) {
+gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
+               const __grid_constant__ CUtensorMap wmap2, const GemmParams P) {
+    constexpr int kOutCols = GU ? kBN / 2 : kBN;        // output columns (weight rows of one projection) per tile
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                    // swizzled tiles want 1024-byte alignment
@@ -305,11 +312,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     auto drain = [&](int tile, int cbegin, int cstep) {
         const int q = warp & 3;
         const int m0 = (tile % P.tiles_m) * kBT;
-        const int n = (tile / P.tiles_m) * kBN + q * 32 + lane;
+        const int row = q * 32 + lane;                              // TMEM lane
+        const int n = (tile / P.tiles_m) * kOutCols + (GU ? (row >> 1) : row);
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-        const bool nlive = n < P.N;
+        const bool nlive = n < P.N && (!GU || (lane & 1) == 0);      // fused gate/up: the gate lane stores
         float bias = 0.f;
-        if (nlive && P.bias != nullptr)
+        if (!GU && nlive && P.bias != nullptr)
             bias = BF ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.bias)[n]) : __half2float(P.bias[n]);
 #pragma unroll 1
         for (int c0 = 32 * cbegin; c0 < kBT; c0 += 32 * cstep) {
@@ -323,12 +331,19 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                            "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                          : "r"(taddr + (uint32_t)c0));
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if constexpr (GU) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {                       // silu(gate) * up: the up value sits in the next lane
+                    const float up = __shfl_xor_sync(0xffffffffu, __uint_as_float(v[j]), 1);
+                    v[j] = __float_as_uint(activate(__uint_as_float(v[j]), CB_ACT_SILU) * up);
+                }
+            }
             if (nlive) {
                 __half* ocol = P.out + (size_t)(m0 + c0) * P.N + n;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     if (m0 + c0 + j < P.M) {
-                        const float y = activate(__uint_as_float(v[j]) + bias, P.act);
+                        const float y = GU ? __uint_as_float(v[j]) : activate(__uint_as_float(v[j]) + bias, P.act);
                         if constexpr (BF) reinterpret_cast<__nv_bfloat16*>(ocol)[(size_t)j * P.N] = __float2bfloat16_rn(y);
                         else ocol[(size_t)j * P.N] = __float2half_rn(y);
                     }
@@ -372,12 +387,15 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 #endif
             int pit = 0;
             for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x) {
-                const int n0 = (tile / P.tiles_m) * kBN;
+                const int n0 = (tile / P.tiles_m) * kOutCols;
                 for (int sb = 0; sb < nsuper; ++sb, ++pit) {
                     const int slot = pit % kPackedSlots;
                     if (pit >= kPackedSlots && !mbar_wait(empty_p(slot), ((pit / kPackedSlots) - 1) & 1, abort_flag)) { gave_up = 5; break; }
                     mbar_expect_tx(full_p(slot), kBN * kRowBytes);
-                    tma_load_2d(base + kPackedOff + slot * kPackedSlotBytes, &wmap, sb * 2 * kWords, n0, full_p(slot));
+                    const uint32_t dst = base + kPackedOff + slot * kPackedSlotBytes;
+                    tma_load_2d(dst, &wmap, sb * 2 * kWords, n0, full_p(slot));
+                    if constexpr (GU)     // the up projection's 64 rows behind the gate's 64 rows
+                        tma_load_2d(dst + (uint32_t)kOutCols * kRowBytes, &wmap2, sb * 2 * kWords, n0, full_p(slot));
                 }
             }
         }
@@ -442,10 +460,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             if (tl != cur_tile_local) {
                 cur_tile_local = tl;
                 const int tile = blockIdx.x + tl * gridDim.x;
-                const int n = (tile / P.tiles_m) * kBN + r;
+                const int n = (tile / P.tiles_m) * kOutCols + (GU ? (r >> 1) : r);
                 live = n < P.N;
-                srow = reinterpret_cast<const unsigned short*>(P.scales) + (size_t)(live ? n : 0) * P.groups;
-                zrow = reinterpret_cast<const unsigned short*>(P.zeros) + (size_t)(live ? n : 0) * P.groups;
+                const bool second = GU && (r & 1);                       // odd lanes of a fused tile belong to the up projection
+                srow = reinterpret_cast<const unsigned short*>(second ? P.scales2 : P.scales) + (size_t)(live ? n : 0) * P.groups;
+                zrow = reinterpret_cast<const unsigned short*>(second ? P.zeros2 : P.zeros) + (size_t)(live ? n : 0) * P.groups;
             }
             if (!live) return 0u;                                         // rows past N were zero-filled by the copy and get scale 0
             const int g = (kb * kBK) / P.group_size;
@@ -464,7 +483,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             const int half = ((2 * pit) & 3) == grp ? 0 : (((2 * pit + 1) & 3) == grp ? 1 : -1);
             uint32_t w[kWords];
             if (half >= 0) {
-                const unsigned char* stage_words = smem + kPackedOff + slot * kPackedSlotBytes + (uint32_t)r * kRowBytes + half * (kWords * 4);
+                const unsigned char* stage_words = smem + kPackedOff + slot * kPackedSlotBytes + (uint32_t)(GU ? ((r & 1) * kOutCols + (r >> 1)) : r) * kRowBytes + half * (kWords * 4);
                 if constexpr (BITS == 4) {
                     const uint4 a = reinterpret_cast<const uint4*>(stage_words)[0], b4 = reinterpret_cast<const uint4*>(stage_words)[1];
                     w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b4.x; w[5] = b4.y; w[6] = b4.z; w[7] = b4.w;
@@ -584,73 +603,107 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int BITS, bool BF>
-int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const GemmParams& P, int grid, cudaStream_t stream) {
+template <int BITS, bool BF, bool GU>
+int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const CUtensorMap& wmap2, const GemmParams& P, int grid,
+             cudaStream_t stream) {
     static bool attr_done[64] = {};
     int dev = 0;
     CB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        CB_CUDA_TRY(cudaFuncSetAttribute(gemm_ws_kernel<BITS, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        CB_CUDA_TRY(cudaFuncSetAttribute(gemm_ws_kernel<BITS, BF, GU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    gemm_ws_kernel<BITS, BF><<<grid, kThreads, kSmemBytes, stream>>>(xmap, wmap, P);
+    gemm_ws_kernel<BITS, BF, GU><<<grid, kThreads, kSmemBytes, stream>>>(xmap, wmap, wmap2, P);
     CB_CUDA_TRY(cudaGetLastError());
     return CB_OK;
 }
 
 }  // namespace
 
-// CB_OK after launching; a CB_ERR_* code on a CUDA error; -1 when the problem is outside this kernel's
-// domain (fp16 or bf16, K a multiple of 128, group size a multiple of 64, N a multiple of 8, 16-byte aligned
-// x / packed / out) and the caller should use another kernel.
-int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
-                   int64_t gs, int act, cudaStream_t stream) {
-    if ((dtype != CB_F16 && dtype != CB_BF16) || K % 128 != 0 || gs % kBK != 0 || w->n % 8 != 0 || M < 1) return -1;
+namespace {
+
+// w2 == nullptr: out = act(x W^T + bias).  w2 != nullptr: out = silu(x W^T) * (x W2^T), W and W2 of equal shape.
+int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_weight* w2, void* out, int64_t K, int bits,
+              int64_t gs, int act, cudaStream_t stream) {
+    const bool gu = w2 != nullptr;
+    if ((dtype != CB_F16 && dtype != CB_BF16) || K % 128 != 0 || gs % kBK != 0 || M < 1) return -1;
+    if (!gu && w->n % 8 != 0) return -1;
     if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(w->packed) % 16 ||
-        reinterpret_cast<uintptr_t>(out) % 16)
+        (gu && reinterpret_cast<uintptr_t>(w2->packed) % 16) || reinterpret_cast<uintptr_t>(out) % 2)
         return -1;
     if (M >= (1ll << 31) / 2 || K >= (1ll << 30)) return -1;
     EncodeTiledFn enc = encode_fn();
     if (enc == nullptr) return -1;
     const int sms = sm_count_current();
     if (sms <= 0) return CB_ERR_CUDA;
+    const int out_cols = gu ? kBN / 2 : kBN;                 // weight rows of one projection per tile
 
     const cuuint32_t estr[2] = {1, 1};
-    CUtensorMap xmap, wmap;
-    {   // activations: [M, K] fp16, box 64 x 256, 128-byte swizzle (the UMMA K-major layout)
+    CUtensorMap xmap, wmap, wmap2;
+    {   // activations: [M, K] 16-bit, box 64 x 256, 128-byte swizzle (the UMMA K-major layout)
         const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
         const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
         const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBT};
-        const CUresult cr = enc(&xmap, dtype == CB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
-                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const CUresult cr = enc(&xmap, dtype == CB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                                const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) { set_error("packed_gemm: cuTensorMapEncodeTiled(x) failed (%d)", (int)cr); return CB_ERR_CUDA; }
     }
-    {   // packed words: [N, K/32*bits] uint32, box (128 codes) x 128 rows, no swizzle
+    auto encode_packed = [&](CUtensorMap* map, const cb_weight* pw) -> int {
+        // packed words: [N, K/32*bits] uint32, box (128 codes) x (rows of one projection per tile), no swizzle
         const cuuint64_t wpr = (cuuint64_t)(K / 32) * bits;
-        const cuuint64_t dims[2] = {wpr, (cuuint64_t)w->n};
+        const cuuint64_t dims[2] = {wpr, (cuuint64_t)pw->n};
         const cuuint64_t strides[1] = {wpr * 4};
-        const cuuint32_t box[2] = {(cuuint32_t)(4 * bits), (cuuint32_t)kBN};
-        const CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<int32_t*>(w->packed), dims, strides, box, estr,
+        const cuuint32_t box[2] = {(cuuint32_t)(4 * bits), (cuuint32_t)out_cols};
+        const CUresult cr = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<int32_t*>(pw->packed), dims, strides, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) { set_error("packed_gemm: cuTensorMapEncodeTiled(packed) failed (%d)", (int)cr); return CB_ERR_CUDA; }
-    }
+        return CB_OK;
+    };
+    int rc = encode_packed(&wmap, w);
+    if (rc != CB_OK) return rc;
+    rc = encode_packed(&wmap2, gu ? w2 : w);
+    if (rc != CB_OK) return rc;
 
     GemmParams P{};
     P.scales = reinterpret_cast<const __half*>(w->scales);
     P.zeros = reinterpret_cast<const __half*>(w->zeros);
-    P.bias = reinterpret_cast<const __half*>(w->bias);
+    P.scales2 = reinterpret_cast<const __half*>(gu ? w2->scales : w->scales);
+    P.zeros2 = reinterpret_cast<const __half*>(gu ? w2->zeros : w->zeros);
+    P.bias = gu ? nullptr : reinterpret_cast<const __half*>(w->bias);
     P.out = reinterpret_cast<__half*>(out);
     P.M = (int)M; P.N = (int)w->n; P.K = (int)K;
     P.groups = (int)((K + gs - 1) / gs); P.group_size = (int)gs; P.act = act;
-    P.tiles_m = (int)((M + kBT - 1) / kBT); P.tiles_n = (int)((w->n + kBN - 1) / kBN); P.kblocks = (int)(K / kBK);
+    P.tiles_m = (int)((M + kBT - 1) / kBT); P.tiles_n = (int)((w->n + out_cols - 1) / out_cols); P.kblocks = (int)(K / kBK);
     const int grid = std::min(sms, P.tiles_m * P.tiles_n);
+    const bool bf = dtype == CB_BF16;
+#define CB_WS_LAUNCH(B)                                                                                           \
+    (gu ? (bf ? launch_t<B, true, true>(xmap, wmap, wmap2, P, grid, stream) : launch_t<B, false, true>(xmap, wmap, wmap2, P, grid, stream)) \
+        : (bf ? launch_t<B, true, false>(xmap, wmap, wmap2, P, grid, stream) : launch_t<B, false, false>(xmap, wmap, wmap2, P, grid, stream)))
     switch (bits) {
-        case 2: return dtype == CB_BF16 ? launch_t<2, true>(xmap, wmap, P, grid, stream) : launch_t<2, false>(xmap, wmap, P, grid, stream);
-        case 3: return dtype == CB_BF16 ? launch_t<3, true>(xmap, wmap, P, grid, stream) : launch_t<3, false>(xmap, wmap, P, grid, stream);
-        default: return dtype == CB_BF16 ? launch_t<4, true>(xmap, wmap, P, grid, stream) : launch_t<4, false>(xmap, wmap, P, grid, stream);
+        case 2: return CB_WS_LAUNCH(2);
+        case 3: return CB_WS_LAUNCH(3);
+        default: return CB_WS_LAUNCH(4);
     }
+#undef CB_WS_LAUNCH
+}
+
+}  // namespace
+
+// CB_OK after launching; a CB_ERR_* code on a CUDA error; -1 when the problem is outside this kernel's
+// domain (fp16 or bf16, K a multiple of 128, group size a multiple of 64, N a multiple of 8, 16-byte aligned
+// x / packed) and the caller should use another kernel.
+int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
+                   int64_t gs, int act, cudaStream_t stream) {
+    return launch_ws(dtype, x, M, w, nullptr, out, K, bits, gs, act, stream);
+}
+
+// Fused prefill gate/up: out[M, n] = silu(x Wg^T) * (x Wu^T) in one launch; same return convention.
+int launch_gemm_ws_gate_up(int dtype, const void* x, int64_t M, const cb_weight* gate, const cb_weight* up, void* out,
+                           int64_t K, int bits, int64_t gs, cudaStream_t stream) {
+    if (gate->n != up->n) return -1;
+    return launch_ws(dtype, x, M, gate, up, out, K, bits, gs, 0, stream);
 }
 
 int gemm_ws_status_read_and_clear(int* out) {

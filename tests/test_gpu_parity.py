@@ -439,6 +439,33 @@ def test_fused_gate_up(bits, B, split_k):
     close(fused_gate_up(x, g, u, split_k, 2), ref, torch.float16)
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,n,k,gs", [(9, 384, 256, 128), (300, 1376, 4096, 128), (1024, 1000, 1152, 64)])
+def test_fused_gate_up_prefill_kernel(bits, dtype, M, n, k, gs):
+    """silu(x Wg^T) * (x Wu^T) for a prefill batch in ONE tcgen05 launch (gate and up rows interleaved as neighbouring
+    tensor-memory lanes): against the fp32 reference and against the two-GEMM route it replaces; ragged 64-column
+    tiles (n = 1376 = 21.5 tiles, n = 1000), group 64, fp16 and bf16."""
+    from crispybits_kernels import _C, fused_gate_up
+    g, gd, _ = cached(n, k, bits, dtype, False, 1, gs, 0.02)
+    u, ud, _ = cached(n, k, bits, dtype, False, 2, gs, 0.02)
+    x = torch.randn(M, k, device=DEV, dtype=dtype, generator=torch.Generator(DEV).manual_seed(M + n))
+    direct = _C.fused_gate_up_gemm(x, g.packed, g.scales, g.zeros, u.packed, u.scales, u.zeros, bits, k, gs)
+    assert direct is not None and direct.shape == (M, n) and direct.dtype == dtype     # the fused kernel took the call
+    y = fused_gate_up(x, g, u, decode_threshold=0)
+    assert torch.equal(y, direct)
+    ref = torch.nn.functional.silu(x.float() @ gd.T) * (x.float() @ ud.T)
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3                       # a product of two rounded-weight GEMMs
+    assert rel_err(y, ref) < tol
+    _C.set_option(1, 1)                                                   # CUDA-core kernels: two GEMMs and a product
+    try:
+        two = fused_gate_up(x, g, u, decode_threshold=0)
+    finally:
+        _C.set_option(1, 0)
+    assert rel_err(y, two.float()) < (2e-2 if dtype == torch.bfloat16 else 3e-3)
+    assert _C.decode_status() == 0
+
+
 def test_fused_gate_up_prefill_route():
     from crispybits_kernels import fused_gate_up
     g, gd, _ = cached(384, 256, 4, torch.float16, False, 1)
