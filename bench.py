@@ -411,9 +411,30 @@ def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False
     g = torch.Generator().manual_seed(2)
     x_host = torch.randn(batch, st.d_model, generator=g).half().pin_memory()
     x = x_host.to(device)
-    for _ in range(2):
-        y = st.step(x)
-    torch.cuda.synchronize()
+    comm_note = None
+    try:
+        for _ in range(2):
+            y = st.step(x)
+        torch.cuda.synchronize()
+        ok = 1.0
+    except Exception as exc:      # e.g. peer-mapped memory cannot be set up on this box
+        comm_note = f"{type(exc).__name__}: {exc}"[:200]
+        ok = 0.0
+    if world > 1 and st.comm != "nccl":
+        # every rank must take the same path: if the peer-memory set-up failed anywhere, all ranks use NCCL, and the
+        # line says so
+        all_ok = -reduce_max(-ok)
+        if all_ok < 1.0:
+            print(f"[bench] rank {rank}: peer-store gather unavailable ({comm_note}); using the NCCL gather", file=sys.stderr)
+            st.comm = "nccl"
+            comm_note = comm_note or "peer set-up failed on another rank"
+            for _ in range(2):
+                y = st.step(x)
+            torch.cuda.synchronize()
+        else:
+            comm_note = None
+    elif ok < 1.0:
+        raise RuntimeError(comm_note)
     assert torch.isfinite(y.float()).all(), "decode stack produced non-finite values"
     graph, mode = None, "eager launches"
     try:
@@ -483,7 +504,8 @@ def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False
         "ms_per_step": total_ms / args.steps, "us_per_launch": total_ms * 1e3 / args.steps / st.launches_per_step(),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "decode_stack_llama2_7b_32blocks", "batch": batch, "bitmap_seed": 0,
-                   "mean_bits": float(np.mean(st.bitmap)), "parallelism": (f"column-parallel N over {world} GPUs, " + COMM_TEXT[st.comm]) if world > 1 else "single GPU",
+                   "mean_bits": float(np.mean(st.bitmap)), "parallelism": (f"column-parallel N over {world} GPUs, " + COMM_TEXT[st.comm]
+                                   + (f" [requested {args.comm}: {comm_note}]" if comm_note else "")) if world > 1 else "single GPU",
                    "l2": f"inputs larger than L2: {my_bytes / 1e6:.0f} MB of weights per rank and step", "launch": mode},
         "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
                      "frac": value / world / hbm_peak, "traffic": None, "kernel": "decode step, per GPU",
