@@ -401,6 +401,27 @@ def test_prefill_gemm_bf16_tensor_core_kernel(bits, M, n, k, gs):
     assert _C.decode_status() == 0
 
 
+@pytest.mark.parametrize("bits", [3, 4])
+@pytest.mark.parametrize("M,n,k", [(128, 12288, 4096), (512, 22016, 4096), (4096, 4096, 11008), (1024, 4096, 4096)])
+def test_prefill_gemm_at_the_benchmark_shapes(bits, M, n, k):
+    """The prefill configuration's own (M, N, K) corners: the tensor-core result against the CUDA-core kernel with the
+    same rounded-weight numerics, and linearity in x (a size-independent property: f(2x) = 2 f(x) bit for bit, except
+    where f(x) is an fp16 subnormal, whose rounding step does not scale -- hence the 2^-23 allowance)."""
+    from crispybits_kernels import _C, packed_linear
+    w, _, _ = cached(n, k, bits, torch.float16, False, 17, 128, 0.02)
+    x = (torch.randn(M, k, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(M)) * 0.25)
+    y = packed_linear(x, w, decode_threshold=0)
+    twice = packed_linear(x * 2, w, decode_threshold=0)
+    assert (twice.float() - 2 * y.float()).abs().max().item() <= 2.0 ** -23
+    _C.set_option(1, 1)
+    try:
+        slow = packed_linear(x, w, decode_threshold=0)
+    finally:
+        _C.set_option(1, 0)
+    assert rel_err(y, slow.float()) < 1e-3
+    assert _C.decode_status() == 0
+
+
 @pytest.mark.parametrize("M,n,k", [(300, 4096, 4096), (1024, 1000, 11008)])
 def test_prefill_gemm_is_stable_over_repeated_launches(M, n, k):
     """Shapes with fewer tiles than SMs, where the kernel's roles run at other relative speeds than in the large
