@@ -159,6 +159,17 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out,
 int cb_fused_gate_up_gemm(const void* x, int64_t M, const cb_weight* gate, const cb_weight* up, void* out,
                           int64_t K, int bits, int64_t group_size, int dtype, void* stream);
 
+/* Fused prefill Q/K/V: the three projections of x[M,K] in one tcgen05 launch, with the bias, the rotary embedding
+ * of Q and K (rope_cos / rope_sin [M, head_dim] float32, or NULL for none) and the un-permuted store in the
+ * epilogue -- the prefill counterpart of cb_fused_qkv, same argument meaning.  The reference runs three GEMMs,
+ * a column gather and a separate rotation here (Crispybits/Kernel/crispybits_kernels/ops.py:268-272).  Returns
+ * CB_ERR_UNSUPPORTED outside the kernel's domain (fp16 / bf16, K and every projection's rows multiples of 128,
+ * group size a multiple of 64); the caller then uses cb_packed_gemm per projection. */
+int cb_fused_qkv_gemm(const void* x, int64_t M, const cb_weight* q, const cb_weight* k, const cb_weight* v,
+                      void* out_q, void* out_k, void* out_v, const float* rope_cos, const float* rope_sin,
+                      int64_t head_dim, int64_t perm_hd, int64_t K, int bits, int64_t group_size, int dtype,
+                      void* stream);
+
 /* Bit-exact unpack  codes[n,K] (int32) <- packed[n, ceil(K/32)*bits]; the device counterpart of
  * unpack_codes (Crispybits/Kernel/crispybits_kernels/reference.py:58-67; csrc/bitpack.cuh:10-18),
  * exported so that the integer layout can be checked bit-for-bit against the oracle. */

@@ -428,6 +428,58 @@ def fused_gate_up_gemm(x, wg, sg, zg, wu, su, zu, bits, in_features, group_size)
     return out
 
 
+_lib.cb_fused_qkv_gemm.argtypes = [_vp, _i64, _WP, _WP, _WP, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _i64, _int, _vp]
+_lib.cb_fused_qkv_gemm.restype = _int
+
+
+def fused_qkv_gemm(x, wq, sq, zq, bq, wk, sk, zk, bk, wv, sv, zv, bv, rope_cos, rope_sin, head_dim, perm_hd,
+                   bits, in_features, group_size):
+    """Q, K, V of a prefill batch (+ bias, + RoPE on Q and K, outputs in the original column order) in one launch,
+    or None when the shape is outside the fused kernel's domain (every projection's rows a multiple of 128); the
+    caller then runs three GEMMs and rotates afterwards, as the reference does."""
+    bits, k, gs = int(bits), int(in_features), int(group_size)
+    head_dim, perm_hd = int(head_dim), int(perm_hd)
+    _check_x(x, k)
+    _check_weight(x, wq, sq, zq, bits, k, gs, "fused_qkv_gemm(q)")
+    _check_weight(x, wk, sk, zk, bits, k, gs, "fused_qkv_gemm(k)")
+    _check_weight(x, wv, sv, zv, bits, k, gs, "fused_qkv_gemm(v)")
+    if x.dtype not in (torch.float16, torch.bfloat16) or k % 128 or gs % 64:
+        return None
+    if any(w.shape[0] % 128 for w in (wq, wk, wv)):
+        return None
+    M = x.shape[0]
+    if perm_hd > 0:
+        if perm_hd % 2:
+            _fail("perm head_dim must be even")
+        if wq.shape[0] % perm_hd or wk.shape[0] % perm_hd:
+            _fail("Q/K widths must be multiples of head_dim")
+    rope = rope_cos is not None and rope_cos.numel() > 0
+    rc = rs = None
+    if rope:
+        if not (perm_hd > 0 and perm_hd == head_dim):
+            _fail("fused RoPE needs Q/K weights stored pair-interleaved with the same head_dim "
+                  "(ops.permute_for_rope / install_bitmap(fuse_rope=True))")
+        if rope_cos.shape != rope_sin.shape:
+            _fail("cos/sin shape mismatch")
+        if rope_cos.numel() != M * head_dim:
+            _fail("cos/sin must be [M, head_dim] (one row per x row)")
+        rc = rope_cos.to(device=x.device, dtype=torch.float32).contiguous()
+        rs = rope_sin.to(device=x.device, dtype=torch.float32).contiguous()
+    bq, bk, bv = (_bias_or_none(b, x, w.shape[0]) for b, w in ((bq, wq), (bk, wk), (bv, wv)))
+    outs = [torch.empty((M, w.shape[0]), dtype=x.dtype, device=x.device) for w in (wq, wk, wv)]
+    if M == 0:
+        return outs
+    with torch.cuda.device(x.device):
+        q, kk, v = _weight(wq, sq, zq, bq), _weight(wk, sk, zk, bk), _weight(wv, sv, zv, bv)
+        code = _lib.cb_fused_qkv_gemm(x.data_ptr(), M, ctypes.byref(q), ctypes.byref(kk), ctypes.byref(v),
+                                      outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), _ptr(rc), _ptr(rs),
+                                      head_dim, perm_hd, k, bits, gs, _DTYPE[x.dtype], _stream(x))
+    if code == 3:        # CB_ERR_UNSUPPORTED
+        return None
+    _rc(code)
+    return outs
+
+
 _lib.cb_quantize_pack.argtypes = [_vp, _int, _i64, _i64, _int, _i64, _vp, _vp, _vp, _int, _vp]
 _lib.cb_quantize_pack.restype = _int
 

@@ -345,10 +345,22 @@ def fused_qkv(x: torch.Tensor, q: PackedLinearWeight, k: PackedLinearWeight, v: 
                                   rc, rs, hd, perm, q.bits, q.in_features, q.group_size, split, rho,
                                   _ws_arg(workspace, x2))
     else:
-        oq, ok, ov = (_unpermute_cols(_packed_linear_raw(x2, w, decode_threshold=0), w) for w in (q, k, v))
-        if rope is not None:
-            oq = apply_rope_reference(oq, cos2, sin2, head_dim)
-            ok = apply_rope_reference(ok, cos2, sin2, head_dim)
+        fused, fused_fn = None, getattr(_C, "fused_qkv_gemm", None)
+        if fused_fn is not None:
+            # one launch with bias, rotation and un-permuted stores in the epilogue (None outside its domain)
+            fused = fused_fn(x2, q.packed, q.scales, q.zeros, _bias_arg(q, x2),
+                             k.packed, k.scales, k.zeros, _bias_arg(k, x2),
+                             v.packed, v.scales, v.zeros, _bias_arg(v, x2),
+                             None if rope is None else cos2.float().contiguous(),
+                             None if rope is None else sin2.float().contiguous(),
+                             0 if rope is None else head_dim, perm, q.bits, q.in_features, q.group_size)
+        if fused is not None:
+            oq, ok, ov = fused
+        else:
+            oq, ok, ov = (_unpermute_cols(_packed_linear_raw(x2, w, decode_threshold=0), w) for w in (q, k, v))
+            if rope is not None:
+                oq = apply_rope_reference(oq, cos2, sin2, head_dim)
+                ok = apply_rope_reference(ok, cos2, sin2, head_dim)
     return (oq.reshape(*lead, q.out_features), ok.reshape(*lead, k.out_features),
             ov.reshape(*lead, v.out_features))
 

@@ -46,6 +46,9 @@ int gemm_status_read_and_clear(int* out);
 int gemm_ws_status_read_and_clear(int* out);
 int launch_gemm_ws_gate_up(int dtype, const void* x, int64_t M, const cb_weight* gate, const cb_weight* up, void* out,
                            int64_t K, int bits, int64_t gs, cudaStream_t stream);
+int launch_gemm_ws_qkv(int dtype, const void* x, int64_t M, const cb_weight* q, const cb_weight* k, const cb_weight* v,
+                       void* out_q, void* out_k, void* out_v, const float* rope_cos, const float* rope_sin, int head_dim,
+                       int perm_hd, int64_t K, int bits, int64_t gs, cudaStream_t stream);
 int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
                    int64_t gs, int act, cudaStream_t stream);
 int launch_gemm_tc(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
@@ -412,6 +415,38 @@ int cb_fused_gate_up_gemm(const void* x, int64_t M, const cb_weight* gate, const
         if (rc2 != -1) return rc2;
     }
     set_error("fused_gate_up_gemm: outside the fused kernel's domain (fp16 / bf16, K a multiple of 128, group size a multiple of 64)");
+    return CB_ERR_UNSUPPORTED;
+}
+
+int cb_fused_qkv_gemm(const void* x, int64_t M, const cb_weight* q, const cb_weight* k, const cb_weight* v,
+                      void* out_q, void* out_k, void* out_v, const float* rope_cos, const float* rope_sin,
+                      int64_t head_dim, int64_t perm_hd, int64_t K, int bits, int64_t group_size, int dtype, void* stream) {
+    int rc = check_common("fused_qkv_gemm", x, M, K, bits, group_size, dtype);
+    if (rc) return rc;
+    if ((rc = check_weight("fused_qkv_gemm(q)", q, bits))) return rc;
+    if ((rc = check_weight("fused_qkv_gemm(k)", k, bits))) return rc;
+    if ((rc = check_weight("fused_qkv_gemm(v)", v, bits))) return rc;
+    CB_REQUIRE(perm_hd >= 0, "fused_qkv_gemm: perm head_dim must be >= 0");
+    if (perm_hd > 0) {
+        CB_REQUIRE(perm_hd % 2 == 0, "fused_qkv_gemm: perm head_dim must be even");
+        CB_REQUIRE(q->n % perm_hd == 0 && k->n % perm_hd == 0, "fused_qkv_gemm: Q/K widths must be multiples of head_dim");
+    }
+    const bool rope = rope_cos != nullptr;
+    if (rope) {
+        CB_REQUIRE(rope_sin != nullptr, "fused_qkv_gemm: cos given without sin");
+        CB_REQUIRE(perm_hd > 0 && perm_hd == head_dim,
+                   "fused_qkv_gemm: fused RoPE needs Q/K stored pair-interleaved with the same head_dim");
+    }
+    if (M == 0) return CB_OK;
+    CB_REQUIRE(out_q && out_k && out_v, "fused_qkv_gemm: an output pointer is NULL");
+    if (!g_force_generic) {
+        const int rc2 = launch_gemm_ws_qkv(dtype, x, M, q, k, v, out_q, out_k, out_v, rope ? rope_cos : nullptr,
+                                           rope ? rope_sin : nullptr, (int)head_dim, (int)perm_hd, K, bits, group_size,
+                                           reinterpret_cast<cudaStream_t>(stream));
+        if (rc2 != -1) return rc2;
+    }
+    set_error("fused_qkv_gemm: outside the fused kernel's domain (fp16 / bf16, K and every projection's rows multiples "
+              "of 128, group size a multiple of 64)");
     return CB_ERR_UNSUPPORTED;
 }
 

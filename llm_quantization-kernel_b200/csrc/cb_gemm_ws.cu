@@ -52,6 +52,11 @@ __device__ int g_gemm_ws_status;   // 0 = ok, else the role that gave up waiting
 struct GemmParams {
     const __half* scales; const __half* zeros; const __half* bias; __half* out;
     const __half* scales2; const __half* zeros2;     // fused gate/up: the up projection's metadata (scales / zeros are the gate's)
+    // fused Q/K/V: projections 2 and 3 (K, V); scales / zeros / bias / out / n1 are Q's
+    const __half* scales3; const __half* zeros3; const __half* bias2; const __half* bias3; __half* out2; __half* out3;
+    int n1, n2, n3;                                  // rows of Q, K, V (each a multiple of 128)
+    const float* rope_cos; const float* rope_sin;    // [M, head_dim] fp32 or nullptr
+    int head_dim, perm_hd;
     int M, N, K, groups, group_size, act;
     int tiles_m, tiles_n, kblocks;
 };
@@ -253,10 +258,22 @@ template <> struct Dequant16B<3> {
 // interleaved (lane 2i = gate row n0 + i, lane 2i + 1 = up row n0 + i), so that silu(gate) * up is a product of
 // neighbouring lanes in the epilogue (the virtual-row trick of the decode kernel,
 // Crispybits/Kernel/csrc/packed_gemv.cu:33-42, 61-64); a tile then covers 64 output columns.
-template <int BITS, bool BF, bool GU>
+// MODE 2: fused Q/K/V.  Tiles run over the rows of Q, then K, then V (each projection a whole number of tiles);
+// the epilogue adds the bias, rotates Q and K (RoPE with the partner row in the neighbouring lane -- the rows are
+// stored pair-interleaved, Crispybits/Kernel/csrc/common.cuh:61-70) and writes at the un-permuted column of the
+// projection's own output.
+template <int BITS, bool BF, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
-               const __grid_constant__ CUtensorMap wmap2, const GemmParams P) {
+               const __grid_constant__ CUtensorMap wmap2, const __grid_constant__ CUtensorMap wmap3, const GemmParams P) {
+    constexpr bool GU = MODE == 1, QKV = MODE == 2;
+    // fused Q/K/V: projection and first row (inside the projection) of weight tile tn
+    auto tile_proj = [&](int tn, int& proj, int& n0) {
+        const int tq = P.n1 / kBN, tk = P.n2 / kBN;
+        if (tn < tq) { proj = 0; n0 = tn * kBN; }
+        else if (tn < tq + tk) { proj = 1; n0 = (tn - tq) * kBN; }
+        else { proj = 2; n0 = (tn - tq - tk) * kBN; }
+    };
     constexpr int kOutCols = GU ? kBN / 2 : kBN;        // output columns (weight rows of one projection) per tile
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -313,12 +330,36 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         const int q = warp & 3;
         const int m0 = (tile % P.tiles_m) * kBT;
         const int row = q * 32 + lane;                              // TMEM lane
-        const int n = (tile / P.tiles_m) * kOutCols + (GU ? (row >> 1) : row);
+        int n = (tile / P.tiles_m) * kOutCols + (GU ? (row >> 1) : row);
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-        const bool nlive = n < P.N && (!GU || (lane & 1) == 0);      // fused gate/up: the gate lane stores
+        bool nlive = n < P.N && (!GU || (lane & 1) == 0);            // fused gate/up: the gate lane stores
+        auto load_bias = [&](const __half* b, int r) {
+            return b == nullptr ? 0.f
+                   : BF ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(b)[r]) : __half2float(b[r]);
+        };
         float bias = 0.f;
-        if (!GU && nlive && P.bias != nullptr)
-            bias = BF ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.bias)[n]) : __half2float(P.bias[n]);
+        __half* obase = P.out;
+        int ld = P.N;                                               // row stride of the output
+        // fused Q/K/V: the projection's output, the un-permuted column, the partner's bias and the RoPE column
+        float bias_partner = 0.f;
+        int rope_d = -1;
+        if constexpr (QKV) {
+            int proj, pn0;
+            tile_proj(tile / P.tiles_m, proj, pn0);
+            const int r = pn0 + row;
+            const __half* b = proj == 0 ? P.bias : proj == 1 ? P.bias2 : P.bias3;
+            obase = proj == 0 ? P.out : proj == 1 ? P.out2 : P.out3;
+            ld = proj == 0 ? P.n1 : proj == 1 ? P.n2 : P.n3;
+            bias = load_bias(b, r);
+            n = unpermute_row(r, proj < 2 ? P.perm_hd : 0);
+            nlive = true;
+            if (P.rope_cos != nullptr && proj < 2) {
+                bias_partner = load_bias(b, r ^ 1);
+                rope_d = n % P.head_dim;
+            }
+        } else if (!GU && nlive) {
+            bias = load_bias(P.bias, n);
+        }
 #pragma unroll 1
         for (int c0 = 32 * cbegin; c0 < kBT; c0 += 32 * cstep) {
             uint32_t v[32];
@@ -338,14 +379,31 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     v[j] = __float_as_uint(activate(__uint_as_float(v[j]), CB_ACT_SILU) * up);
                 }
             }
+            if constexpr (QKV) {
+                if (__any_sync(0xffffffffu, rope_d >= 0)) {          // uniform over the warp: one projection per tile
+                    const bool first_half = rope_d < P.head_dim / 2;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {                   // the rotation partner sits in the next lane
+                        const float y = __uint_as_float(v[j]) + bias;
+                        const float yp = __shfl_xor_sync(0xffffffffu, __uint_as_float(v[j]), 1) + bias_partner;
+                        const int m = min(m0 + c0 + j, P.M - 1);
+                        const float c = P.rope_cos[(size_t)m * P.head_dim + rope_d];
+                        const float sn = P.rope_sin[(size_t)m * P.head_dim + rope_d];
+                        v[j] = __float_as_uint(first_half ? (y * c - yp * sn) : (y * c + yp * sn));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + bias);
+                }
+            }
             if (nlive) {
-                __half* ocol = P.out + (size_t)(m0 + c0) * P.N + n;
+                __half* ocol = obase + (size_t)(m0 + c0) * ld + n;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     if (m0 + c0 + j < P.M) {
-                        const float y = GU ? __uint_as_float(v[j]) : activate(__uint_as_float(v[j]) + bias, P.act);
-                        if constexpr (BF) reinterpret_cast<__nv_bfloat16*>(ocol)[(size_t)j * P.N] = __float2bfloat16_rn(y);
-                        else ocol[(size_t)j * P.N] = __float2half_rn(y);
+                        const float y = (GU || QKV) ? __uint_as_float(v[j]) : activate(__uint_as_float(v[j]) + bias, P.act);
+                        if constexpr (BF) reinterpret_cast<__nv_bfloat16*>(ocol)[(size_t)j * ld] = __float2bfloat16_rn(y);
+                        else ocol[(size_t)j * ld] = __float2half_rn(y);
                     }
                 }
             }
@@ -387,13 +445,19 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 #endif
             int pit = 0;
             for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x) {
-                const int n0 = (tile / P.tiles_m) * kOutCols;
+                int n0 = (tile / P.tiles_m) * kOutCols;
+                const CUtensorMap* map = &wmap;
+                if constexpr (QKV) {      // the tile's projection has its own packed tensor
+                    int proj;
+                    tile_proj(tile / P.tiles_m, proj, n0);
+                    map = proj == 0 ? &wmap : proj == 1 ? &wmap2 : &wmap3;
+                }
                 for (int sb = 0; sb < nsuper; ++sb, ++pit) {
                     const int slot = pit % kPackedSlots;
                     if (pit >= kPackedSlots && !mbar_wait(empty_p(slot), ((pit / kPackedSlots) - 1) & 1, abort_flag)) { gave_up = 5; break; }
                     mbar_expect_tx(full_p(slot), kBN * kRowBytes);
                     const uint32_t dst = base + kPackedOff + slot * kPackedSlotBytes;
-                    tma_load_2d(dst, &wmap, sb * 2 * kWords, n0, full_p(slot));
+                    tma_load_2d(dst, map, sb * 2 * kWords, n0, full_p(slot));
                     if constexpr (GU)     // the up projection's 64 rows behind the gate's 64 rows
                         tma_load_2d(dst + (uint32_t)kOutCols * kRowBytes, &wmap2, sb * 2 * kWords, n0, full_p(slot));
                 }
@@ -460,11 +524,19 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             if (tl != cur_tile_local) {
                 cur_tile_local = tl;
                 const int tile = blockIdx.x + tl * gridDim.x;
-                const int n = (tile / P.tiles_m) * kOutCols + (GU ? (r >> 1) : r);
+                int n = (tile / P.tiles_m) * kOutCols + (GU ? (r >> 1) : r);
                 live = n < P.N;
-                const bool second = GU && (r & 1);                       // odd lanes of a fused tile belong to the up projection
-                srow = reinterpret_cast<const unsigned short*>(second ? P.scales2 : P.scales) + (size_t)(live ? n : 0) * P.groups;
-                zrow = reinterpret_cast<const unsigned short*>(second ? P.zeros2 : P.zeros) + (size_t)(live ? n : 0) * P.groups;
+                int proj = (GU && (r & 1)) ? 1 : 0;                      // odd lanes of a fused gate/up tile belong to the up projection
+                if constexpr (QKV) {
+                    int pn0;
+                    tile_proj(tile / P.tiles_m, proj, pn0);
+                    n = pn0 + r;
+                    live = true;
+                }
+                const __half* sc = proj == 0 ? P.scales : proj == 1 ? P.scales2 : P.scales3;
+                const __half* zr = proj == 0 ? P.zeros : proj == 1 ? P.zeros2 : P.zeros3;
+                srow = reinterpret_cast<const unsigned short*>(sc) + (size_t)(live ? n : 0) * P.groups;
+                zrow = reinterpret_cast<const unsigned short*>(zr) + (size_t)(live ? n : 0) * P.groups;
             }
             if (!live) return 0u;                                         // rows past N were zero-filled by the copy and get scale 0
             const int g = (kb * kBK) / P.group_size;
@@ -603,17 +675,17 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int BITS, bool BF, bool GU>
-int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const CUtensorMap& wmap2, const GemmParams& P, int grid,
-             cudaStream_t stream) {
+template <int BITS, bool BF, int MODE>
+int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const CUtensorMap& wmap2, const CUtensorMap& wmap3,
+             const GemmParams& P, int grid, cudaStream_t stream) {
     static bool attr_done[64] = {};
     int dev = 0;
     CB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        CB_CUDA_TRY(cudaFuncSetAttribute(gemm_ws_kernel<BITS, BF, GU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        CB_CUDA_TRY(cudaFuncSetAttribute(gemm_ws_kernel<BITS, BF, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    gemm_ws_kernel<BITS, BF, GU><<<grid, kThreads, kSmemBytes, stream>>>(xmap, wmap, wmap2, P);
+    gemm_ws_kernel<BITS, BF, MODE><<<grid, kThreads, kSmemBytes, stream>>>(xmap, wmap, wmap2, wmap3, P);
     CB_CUDA_TRY(cudaGetLastError());
     return CB_OK;
 }
@@ -623,14 +695,26 @@ int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const CUtensorMap
 namespace {
 
 // w2 == nullptr: out = act(x W^T + bias).  w2 != nullptr: out = silu(x W^T) * (x W2^T), W and W2 of equal shape.
+// qkv != nullptr: w, qkv->k, qkv->v are the Q, K, V projections; out is Q's output.
+struct WsQkv {
+    const cb_weight* k; const cb_weight* v;
+    void* out_k; void* out_v;
+    const float* rope_cos; const float* rope_sin;
+    int head_dim, perm_hd;
+};
+
 int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_weight* w2, void* out, int64_t K, int bits,
-              int64_t gs, int act, cudaStream_t stream) {
-    const bool gu = w2 != nullptr;
+              int64_t gs, int act, cudaStream_t stream, const WsQkv* qkv = nullptr) {
+    const bool gu = w2 != nullptr && qkv == nullptr;
     if ((dtype != CB_F16 && dtype != CB_BF16) || K % 128 != 0 || gs % kBK != 0 || M < 1) return -1;
     if (!gu && w->n % 8 != 0) return -1;
     if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(w->packed) % 16 ||
         (gu && reinterpret_cast<uintptr_t>(w2->packed) % 16) || reinterpret_cast<uintptr_t>(out) % 2)
         return -1;
+    if (qkv != nullptr) {     // every projection a whole number of tiles, so that a tile has one projection
+        if (w->n % kBN != 0 || qkv->k->n % kBN != 0 || qkv->v->n % kBN != 0) return -1;
+        if (reinterpret_cast<uintptr_t>(qkv->k->packed) % 16 || reinterpret_cast<uintptr_t>(qkv->v->packed) % 16) return -1;
+    }
     if (M >= (1ll << 31) / 2 || K >= (1ll << 30)) return -1;
     EncodeTiledFn enc = encode_fn();
     if (enc == nullptr) return -1;
@@ -639,7 +723,7 @@ int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_
     const int out_cols = gu ? kBN / 2 : kBN;                 // weight rows of one projection per tile
 
     const cuuint32_t estr[2] = {1, 1};
-    CUtensorMap xmap, wmap, wmap2;
+    CUtensorMap xmap, wmap, wmap2, wmap3;
     {   // activations: [M, K] 16-bit, box 64 x 256, 128-byte swizzle (the UMMA K-major layout)
         const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
         const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
@@ -663,7 +747,9 @@ int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_
     };
     int rc = encode_packed(&wmap, w);
     if (rc != CB_OK) return rc;
-    rc = encode_packed(&wmap2, gu ? w2 : w);
+    rc = encode_packed(&wmap2, gu ? w2 : qkv ? qkv->k : w);
+    if (rc != CB_OK) return rc;
+    rc = encode_packed(&wmap3, qkv ? qkv->v : w);
     if (rc != CB_OK) return rc;
 
     GemmParams P{};
@@ -676,17 +762,32 @@ int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_
     P.M = (int)M; P.N = (int)w->n; P.K = (int)K;
     P.groups = (int)((K + gs - 1) / gs); P.group_size = (int)gs; P.act = act;
     P.tiles_m = (int)((M + kBT - 1) / kBT); P.tiles_n = (int)((w->n + out_cols - 1) / out_cols); P.kblocks = (int)(K / kBK);
+    if (qkv != nullptr) {
+        P.bias = reinterpret_cast<const __half*>(w->bias);
+        P.scales2 = reinterpret_cast<const __half*>(qkv->k->scales); P.zeros2 = reinterpret_cast<const __half*>(qkv->k->zeros);
+        P.scales3 = reinterpret_cast<const __half*>(qkv->v->scales); P.zeros3 = reinterpret_cast<const __half*>(qkv->v->zeros);
+        P.bias2 = reinterpret_cast<const __half*>(qkv->k->bias); P.bias3 = reinterpret_cast<const __half*>(qkv->v->bias);
+        P.out2 = reinterpret_cast<__half*>(qkv->out_k); P.out3 = reinterpret_cast<__half*>(qkv->out_v);
+        P.n1 = (int)w->n; P.n2 = (int)qkv->k->n; P.n3 = (int)qkv->v->n;
+        P.N = P.n1 + P.n2 + P.n3;
+        P.tiles_n = P.N / kBN;
+        P.rope_cos = qkv->rope_cos; P.rope_sin = qkv->rope_sin;
+        P.head_dim = qkv->head_dim; P.perm_hd = qkv->perm_hd;
+        P.act = 0;
+    }
     const int grid = std::min(sms, P.tiles_m * P.tiles_n);
     const bool bf = dtype == CB_BF16;
-#define CB_WS_LAUNCH(B)                                                                                           \
-    (gu ? (bf ? launch_t<B, true, true>(xmap, wmap, wmap2, P, grid, stream) : launch_t<B, false, true>(xmap, wmap, wmap2, P, grid, stream)) \
-        : (bf ? launch_t<B, true, false>(xmap, wmap, wmap2, P, grid, stream) : launch_t<B, false, false>(xmap, wmap, wmap2, P, grid, stream)))
+    const int mode = qkv != nullptr ? 2 : gu ? 1 : 0;
+#define CB_WS_LAUNCH_M(B, MD) \
+    (bf ? launch_t<B, true, MD>(xmap, wmap, wmap2, wmap3, P, grid, stream) : launch_t<B, false, MD>(xmap, wmap, wmap2, wmap3, P, grid, stream))
+#define CB_WS_LAUNCH(B) (mode == 2 ? CB_WS_LAUNCH_M(B, 2) : mode == 1 ? CB_WS_LAUNCH_M(B, 1) : CB_WS_LAUNCH_M(B, 0))
     switch (bits) {
         case 2: return CB_WS_LAUNCH(2);
         case 3: return CB_WS_LAUNCH(3);
         default: return CB_WS_LAUNCH(4);
     }
 #undef CB_WS_LAUNCH
+#undef CB_WS_LAUNCH_M
 }
 
 }  // namespace
@@ -704,6 +805,15 @@ int launch_gemm_ws_gate_up(int dtype, const void* x, int64_t M, const cb_weight*
                            int64_t K, int bits, int64_t gs, cudaStream_t stream) {
     if (gate->n != up->n) return -1;
     return launch_ws(dtype, x, M, gate, up, out, K, bits, gs, 0, stream);
+}
+
+// Fused prefill Q/K/V (+ bias, + RoPE on Q and K, un-permuted stores) in one launch; same return convention.
+// Needs every projection's row count to be a multiple of 128.
+int launch_gemm_ws_qkv(int dtype, const void* x, int64_t M, const cb_weight* q, const cb_weight* k, const cb_weight* v,
+                       void* out_q, void* out_k, void* out_v, const float* rope_cos, const float* rope_sin, int head_dim,
+                       int perm_hd, int64_t K, int bits, int64_t gs, cudaStream_t stream) {
+    const WsQkv spec{k, v, out_k, out_v, rope_cos, rope_sin, head_dim, perm_hd};
+    return launch_ws(dtype, x, M, q, k, out_q, K, bits, gs, 0, stream, &spec);
 }
 
 int gemm_ws_status_read_and_clear(int* out) {

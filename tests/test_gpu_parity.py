@@ -522,6 +522,74 @@ def test_fused_qkv_gqa(bits, B, split_k, rope, head_dim, bias):
     close(oq, rq, torch.float16, tol); close(ok, rk, torch.float16, tol); close(ov, rv, torch.float16, tol)
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,nq,nkv,head_dim,rope,bias", [
+    (9, 256, 2, 1, 128, True, True),
+    (300, 1024, 8, 2, 128, True, False),
+    (300, 1024, 8, 2, 64, True, True),
+    (700, 2048, 4, 4, 128, False, True),       # permuted, no rotation
+    (64, 512, 3, 1, 0, False, False),          # natural order
+])
+def test_fused_qkv_prefill_kernel(bits, dtype, M, K, nq, nkv, head_dim, rope, bias):
+    """Q, K, V of a prefill batch in ONE tcgen05 launch (bias, RoPE and the un-permuted store in the epilogue): against
+    the fp32 reference and against the route it replaces (three GEMMs, a column gather, a separate rotation); GQA
+    widths, head_dim 64 and 128, several token tiles, a ragged last token tile."""
+    from crispybits_kernels import _C, apply_rope_reference, fused_qkv, permute_for_rope
+    hd = head_dim or 128
+    q, qd, qb = cached(nq * hd, K, bits, dtype, bias, 1, 128, 0.02)
+    k, kd, kb = cached(nkv * hd, K, bits, dtype, bias, 2, 128, 0.02)
+    v, vd, vb = cached(nkv * hd, K, bits, dtype, bias, 3, 128, 0.02)
+    if head_dim:
+        q, k = permute_for_rope(q, head_dim), permute_for_rope(k, head_dim)
+    x = torch.randn(M, K, device=DEV, dtype=dtype, generator=torch.Generator(DEV).manual_seed(M + K))
+    rq, rk, rv = ref_linear(x, qd, qb), ref_linear(x, kd, kb), ref_linear(x, vd, vb)
+    r, cos, sin = None, None, None
+    if rope:
+        cos, sin = rope_tables(M, head_dim, DEV)
+        rq = apply_rope_reference(rq, cos, sin, head_dim)
+        rk = apply_rope_reference(rk, cos, sin, head_dim)
+        r = (cos, sin, head_dim)
+    e = torch.empty(0, device=DEV, dtype=dtype)
+    direct = _C.fused_qkv_gemm(x, q.packed, q.scales, q.zeros, q.bias if bias else e,
+                               k.packed, k.scales, k.zeros, k.bias if bias else e,
+                               v.packed, v.scales, v.zeros, v.bias if bias else e,
+                               cos, sin, head_dim if rope else 0, head_dim, bits, K, 128)
+    assert direct is not None                                             # the fused kernel took the call
+    got = fused_qkv(x, q, k, v, rope=r, decode_threshold=0)
+    tol = 2e-2 if dtype == torch.bfloat16 else 3e-3
+    for y, d, ref in zip(got, direct, (rq, rk, rv)):
+        assert y.dtype == dtype and torch.equal(y, d)
+        assert rel_err(y, ref) < tol
+    _C.set_option(1, 1)                                                   # CUDA-core kernels: the unfused route
+    try:
+        three = fused_qkv(x, q, k, v, rope=r, decode_threshold=0)
+    finally:
+        _C.set_option(1, 0)
+    for y, t in zip(got, three):
+        assert rel_err(y, t.float()) < tol
+    assert _C.decode_status() == 0
+
+
+def test_fused_qkv_prefill_outside_domain_falls_back():
+    """A projection whose row count is not a multiple of 128 takes the three-GEMM route, with the same results."""
+    from crispybits_kernels import _C, apply_rope_reference, fused_qkv, permute_for_rope
+    K, hd = 512, 64
+    q, qd, _ = cached(3 * hd, K, 4, torch.float16, False, 1)
+    k, kd, _ = cached(hd, K, 4, torch.float16, False, 2)
+    v, vd, _ = cached(hd, K, 4, torch.float16, False, 3)
+    q, k = permute_for_rope(q, hd), permute_for_rope(k, hd)
+    x = torch.randn(40, K, device=DEV, dtype=torch.float16)
+    cos, sin = rope_tables(40, hd, DEV)
+    e = torch.empty(0, device=DEV, dtype=torch.float16)
+    assert _C.fused_qkv_gemm(x, q.packed, q.scales, q.zeros, e, k.packed, k.scales, k.zeros, e,
+                             v.packed, v.scales, v.zeros, e, cos, sin, hd, hd, 4, K, 128) is None
+    oq, ok, ov = fused_qkv(x, q, k, v, rope=(cos, sin, hd))
+    close(oq, apply_rope_reference(ref_linear(x, qd, None), cos, sin, hd), torch.float16, 3e-3)
+    close(ok, apply_rope_reference(ref_linear(x, kd, None), cos, sin, hd), torch.float16, 3e-3)
+    close(ov, ref_linear(x, vd, None), torch.float16, 3e-3)
+
+
 # ------------------------------------------------------------------ error behaviour
 def test_argument_errors():
     import crispybits_kernels as ck
