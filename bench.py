@@ -549,6 +549,36 @@ def bench_gemm(device, tf_peak, peak_kind, m=1024, iters=10):
         out[f"m{m}_{n}x{k}_w{b}"] = {"us": us, "tflops": tf, "frac_of_dense_peak": tf / tf_peak,
                                      "peak_kind": f"of {peak_kind}"}
         del ws, x
+
+    # the fused forms: gate/up (silu(g) * u in the epilogue) and Q/K/V (bias-free, RoPE and un-permuted stores in
+    # the epilogue), both at K = 4096; FLOPs are those of the projections alone
+    def timed(fn, flops):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / iters
+        tf = flops / (us * 1e-6) / 1e12
+        return {"us": us, "tflops": tf, "frac_of_dense_peak": tf / tf_peak, "peak_kind": f"of {peak_kind}"}
+
+    k, hd = 4096, 128
+    x = torch.randn(m, k, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(6))
+    gate = device_copies(synth_weight_numpy(4, 11, 11008, k), device, 1)[0]
+    up = device_copies(synth_weight_numpy(4, 12, 11008, k), device, 1)[0]
+    out[f"m{m}_gate_up_11008x{k}_w4"] = timed(lambda: ck.fused_gate_up(x, gate, up), 2.0 * m * 2 * 11008 * k)
+    del gate, up
+    q, kk, v = (device_copies(synth_weight_numpy(4, 13 + i, 4096, k), device, 1)[0] for i in range(3))
+    q, kk = ck.permute_for_rope(q, hd), ck.permute_for_rope(kk, hd)
+    pos = torch.arange(m, device=device, dtype=torch.float32)[:, None]
+    inv = 10000.0 ** (-torch.arange(0, hd, 2, device=device, dtype=torch.float32) / hd)
+    ang = torch.cat([pos * inv, pos * inv], dim=1)
+    rope = (ang.cos().contiguous(), ang.sin().contiguous(), hd)
+    out[f"m{m}_qkv_rope_12288x{k}_w4"] = timed(lambda: ck.fused_qkv(x, q, kk, v, rope=rope), 2.0 * m * 12288 * k)
     return out
 
 

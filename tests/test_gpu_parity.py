@@ -447,6 +447,33 @@ def test_prefill_gemm_is_stable_over_repeated_launches(M, n, k):
     assert _C.decode_status() == 0
 
 
+@pytest.mark.parametrize("bits", [2, 4])
+def test_fused_prefill_kernels_are_stable_over_repeated_launches(bits):
+    """The fused gate/up and Q/K/V forms of the prefill kernel, 100 launches each on a shape with several tiles per
+    CTA and one with fewer tiles than SMs: every launch reproduces the first bit for bit."""
+    from crispybits_kernels import fused_gate_up, fused_qkv, permute_for_rope
+    for M, n, k in ((1024, 11008, 1024), (300, 1024, 2048)):
+        g, _, _ = cached(n, k, bits, torch.float16, False, 1, 128, 0.02)
+        u, _, _ = cached(n, k, bits, torch.float16, False, 2, 128, 0.02)
+        x = torch.randn(M, k, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(3))
+        first = fused_gate_up(x, g, u, decode_threshold=0)
+        for _ in range(100):
+            assert torch.equal(fused_gate_up(x, g, u, decode_threshold=0), first)
+    from crispybits_kernels import _C
+    for M, nq, nkv, k in ((1024, 32, 8, 1024), (300, 4, 2, 2048)):
+        q, _, _ = cached(nq * 128, k, bits, torch.float16, True, 1, 128, 0.02)
+        kk, _, _ = cached(nkv * 128, k, bits, torch.float16, True, 2, 128, 0.02)
+        v, _, _ = cached(nkv * 128, k, bits, torch.float16, True, 3, 128, 0.02)
+        q, kk = permute_for_rope(q, 128), permute_for_rope(kk, 128)
+        x = torch.randn(M, k, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(4))
+        rope = rope_tables(M, 128, DEV) + (128,)
+        first = fused_qkv(x, q, kk, v, rope=rope, decode_threshold=0)
+        for _ in range(100):
+            again = fused_qkv(x, q, kk, v, rope=rope, decode_threshold=0)
+            assert all(torch.equal(a, b) for a, b in zip(again, first))
+    assert _C.decode_status() == 0
+
+
 # ------------------------------------------------------------------ fused gate/up and QKV
 @pytest.mark.parametrize("bits", [2, 3, 4])
 @pytest.mark.parametrize("B", [1, 4])
