@@ -642,6 +642,14 @@ def test_argument_errors():
         lambda: _C.packed_gemm(x[:, :100].contiguous(), w.packed, w.scales, w.zeros, e, 3, 256, 128, 0, True),
         lambda: _C.fused_qkv(x, w.packed, w.scales, w.zeros, e, w.packed, w.scales, w.zeros, e, w.packed, w.scales,
                              w.zeros, e, cos, sin, 128, 0, 3, 256, 128, 1, 1, ws),                      # rope w/o perm
+        lambda: _C.fused_qkv_gemm(x, w.packed, w.scales, w.zeros, e, w.packed, w.scales, w.zeros, e, w.packed, w.scales,
+                                  w.zeros, e, cos, sin, 128, 0, 3, 256, 128),                           # rope w/o perm
+        lambda: _C.fused_qkv_gemm(x, w.packed, w.scales, w.zeros, e, w.packed, w.scales, w.zeros, e, w.packed, w.scales,
+                                  w.zeros, e, cos[:, :64], sin, 128, 128, 3, 256, 128),                 # cos/sin shapes
+        lambda: _C.fused_qkv_gemm(x, w.packed, w.scales, w.zeros, e, w.packed, w.scales, w.zeros, e, w.packed, w.scales,
+                                  w.zeros, e, None, None, 0, 6, 3, 256, 128),                           # rows not a multiple of head_dim
+        lambda: _C.fused_gate_up_gemm(x, w.packed, w.scales, w.zeros, w.packed[:128], w.scales[:128], w.zeros[:128],
+                                      3, 256, 128),                                                     # gate/up shapes
     ]
     for call in bad:
         with pytest.raises(RuntimeError):
