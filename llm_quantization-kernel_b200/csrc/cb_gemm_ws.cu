@@ -49,14 +49,19 @@ constexpr uint32_t kIdescBF16 = kIdescF16 | (1u << 7) | (1u << 10);
 
 __device__ int g_gemm_ws_status;   // 0 = ok, else the role that gave up waiting (1 x producer, 2 mma, 3 dequant, 4 epilogue, 5 packed producer)
 
-struct GemmParams {
-    const __half* scales; const __half* zeros; const __half* bias; __half* out;
-    const __half* scales2; const __half* zeros2;     // fused gate/up: the up projection's metadata (scales / zeros are the gate's)
-    // fused Q/K/V: projections 2 and 3 (K, V); scales / zeros / bias / out / n1 are Q's
+// Fused Q/K/V only: projections 2 and 3 (K, V); GemmParams' scales / zeros / scales2 / zeros2 / bias / out are Q's and
+// K's.  A kernel parameter of its own: with these fields inside GemmParams the compiler generated other code for the
+// plain kernel (80 instead of 72 registers), measured a fifth slower on shapes with several tiles per CTA.
+struct QkvParams {
     const __half* scales3; const __half* zeros3; const __half* bias2; const __half* bias3; __half* out2; __half* out3;
     int n1, n2, n3;                                  // rows of Q, K, V (each a multiple of 128)
     const float* rope_cos; const float* rope_sin;    // [M, head_dim] fp32 or nullptr
     int head_dim, perm_hd;
+};
+
+struct GemmParams {
+    const __half* scales; const __half* zeros; const __half* bias; __half* out;
+    const __half* scales2; const __half* zeros2;     // fused gate/up: the up projection's metadata (scales / zeros are the gate's)
     int M, N, K, groups, group_size, act;
     int tiles_m, tiles_n, kblocks;
 };
@@ -265,11 +270,11 @@ template <> struct Dequant16B<3> {
 template <int BITS, bool BF, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
-               const __grid_constant__ CUtensorMap wmap2, const __grid_constant__ CUtensorMap wmap3, const GemmParams P) {
+               const __grid_constant__ CUtensorMap wmap2, const __grid_constant__ CUtensorMap wmap3, const GemmParams P, const QkvParams Q) {
     constexpr bool GU = MODE == 1, QKV = MODE == 2;
     // fused Q/K/V: projection and first row (inside the projection) of weight tile tn
     auto tile_proj = [&](int tn, int& proj, int& n0) {
-        const int tq = P.n1 / kBN, tk = P.n2 / kBN;
+        const int tq = Q.n1 / kBN, tk = Q.n2 / kBN;
         if (tn < tq) { proj = 0; n0 = tn * kBN; }
         else if (tn < tq + tk) { proj = 1; n0 = (tn - tq) * kBN; }
         else { proj = 2; n0 = (tn - tq - tk) * kBN; }
@@ -347,15 +352,15 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             int proj, pn0;
             tile_proj(tile / P.tiles_m, proj, pn0);
             const int r = pn0 + row;
-            const __half* b = proj == 0 ? P.bias : proj == 1 ? P.bias2 : P.bias3;
-            obase = proj == 0 ? P.out : proj == 1 ? P.out2 : P.out3;
-            ld = proj == 0 ? P.n1 : proj == 1 ? P.n2 : P.n3;
+            const __half* b = proj == 0 ? P.bias : proj == 1 ? Q.bias2 : Q.bias3;
+            obase = proj == 0 ? P.out : proj == 1 ? Q.out2 : Q.out3;
+            ld = proj == 0 ? Q.n1 : proj == 1 ? Q.n2 : Q.n3;
             bias = load_bias(b, r);
-            n = unpermute_row(r, proj < 2 ? P.perm_hd : 0);
+            n = unpermute_row(r, proj < 2 ? Q.perm_hd : 0);
             nlive = true;
-            if (P.rope_cos != nullptr && proj < 2) {
+            if (Q.rope_cos != nullptr && proj < 2) {
                 bias_partner = load_bias(b, r ^ 1);
-                rope_d = n % P.head_dim;
+                rope_d = n % Q.head_dim;
             }
         } else if (!GU && nlive) {
             bias = load_bias(P.bias, n);
@@ -381,14 +386,14 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             }
             if constexpr (QKV) {
                 if (__any_sync(0xffffffffu, rope_d >= 0)) {          // uniform over the warp: one projection per tile
-                    const bool first_half = rope_d < P.head_dim / 2;
+                    const bool first_half = rope_d < Q.head_dim / 2;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {                   // the rotation partner sits in the next lane
                         const float y = __uint_as_float(v[j]) + bias;
                         const float yp = __shfl_xor_sync(0xffffffffu, __uint_as_float(v[j]), 1) + bias_partner;
                         const int m = min(m0 + c0 + j, P.M - 1);
-                        const float c = P.rope_cos[(size_t)m * P.head_dim + rope_d];
-                        const float sn = P.rope_sin[(size_t)m * P.head_dim + rope_d];
+                        const float c = Q.rope_cos[(size_t)m * Q.head_dim + rope_d];
+                        const float sn = Q.rope_sin[(size_t)m * Q.head_dim + rope_d];
                         v[j] = __float_as_uint(first_half ? (y * c - yp * sn) : (y * c + yp * sn));
                     }
                 } else {
@@ -533,8 +538,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     n = pn0 + r;
                     live = true;
                 }
-                const __half* sc = proj == 0 ? P.scales : proj == 1 ? P.scales2 : P.scales3;
-                const __half* zr = proj == 0 ? P.zeros : proj == 1 ? P.zeros2 : P.zeros3;
+                const __half* sc = proj == 0 ? P.scales : proj == 1 ? P.scales2 : Q.scales3;
+                const __half* zr = proj == 0 ? P.zeros : proj == 1 ? P.zeros2 : Q.zeros3;
                 srow = reinterpret_cast<const unsigned short*>(sc) + (size_t)(live ? n : 0) * P.groups;
                 zrow = reinterpret_cast<const unsigned short*>(zr) + (size_t)(live ? n : 0) * P.groups;
             }
@@ -677,7 +682,7 @@ EncodeTiledFn encode_fn() {
 
 template <int BITS, bool BF, int MODE>
 int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const CUtensorMap& wmap2, const CUtensorMap& wmap3,
-             const GemmParams& P, int grid, cudaStream_t stream) {
+             const GemmParams& P, const QkvParams& Q, int grid, cudaStream_t stream) {
     static bool attr_done[64] = {};
     int dev = 0;
     CB_CUDA_TRY(cudaGetDevice(&dev));
@@ -685,7 +690,7 @@ int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const CUtensorMap
         CB_CUDA_TRY(cudaFuncSetAttribute(gemm_ws_kernel<BITS, BF, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    gemm_ws_kernel<BITS, BF, MODE><<<grid, kThreads, kSmemBytes, stream>>>(xmap, wmap, wmap2, wmap3, P);
+    gemm_ws_kernel<BITS, BF, MODE><<<grid, kThreads, kSmemBytes, stream>>>(xmap, wmap, wmap2, wmap3, P, Q);
     CB_CUDA_TRY(cudaGetLastError());
     return CB_OK;
 }
@@ -753,6 +758,7 @@ int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_
     if (rc != CB_OK) return rc;
 
     GemmParams P{};
+    QkvParams Q{};
     P.scales = reinterpret_cast<const __half*>(w->scales);
     P.zeros = reinterpret_cast<const __half*>(w->zeros);
     P.scales2 = reinterpret_cast<const __half*>(gu ? w2->scales : w->scales);
@@ -765,21 +771,21 @@ int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_
     if (qkv != nullptr) {
         P.bias = reinterpret_cast<const __half*>(w->bias);
         P.scales2 = reinterpret_cast<const __half*>(qkv->k->scales); P.zeros2 = reinterpret_cast<const __half*>(qkv->k->zeros);
-        P.scales3 = reinterpret_cast<const __half*>(qkv->v->scales); P.zeros3 = reinterpret_cast<const __half*>(qkv->v->zeros);
-        P.bias2 = reinterpret_cast<const __half*>(qkv->k->bias); P.bias3 = reinterpret_cast<const __half*>(qkv->v->bias);
-        P.out2 = reinterpret_cast<__half*>(qkv->out_k); P.out3 = reinterpret_cast<__half*>(qkv->out_v);
-        P.n1 = (int)w->n; P.n2 = (int)qkv->k->n; P.n3 = (int)qkv->v->n;
-        P.N = P.n1 + P.n2 + P.n3;
+        Q.scales3 = reinterpret_cast<const __half*>(qkv->v->scales); Q.zeros3 = reinterpret_cast<const __half*>(qkv->v->zeros);
+        Q.bias2 = reinterpret_cast<const __half*>(qkv->k->bias); Q.bias3 = reinterpret_cast<const __half*>(qkv->v->bias);
+        Q.out2 = reinterpret_cast<__half*>(qkv->out_k); Q.out3 = reinterpret_cast<__half*>(qkv->out_v);
+        Q.n1 = (int)w->n; Q.n2 = (int)qkv->k->n; Q.n3 = (int)qkv->v->n;
+        P.N = Q.n1 + Q.n2 + Q.n3;
         P.tiles_n = P.N / kBN;
-        P.rope_cos = qkv->rope_cos; P.rope_sin = qkv->rope_sin;
-        P.head_dim = qkv->head_dim; P.perm_hd = qkv->perm_hd;
+        Q.rope_cos = qkv->rope_cos; Q.rope_sin = qkv->rope_sin;
+        Q.head_dim = qkv->head_dim; Q.perm_hd = qkv->perm_hd;
         P.act = 0;
     }
     const int grid = std::min(sms, P.tiles_m * P.tiles_n);
     const bool bf = dtype == CB_BF16;
     const int mode = qkv != nullptr ? 2 : gu ? 1 : 0;
 #define CB_WS_LAUNCH_M(B, MD) \
-    (bf ? launch_t<B, true, MD>(xmap, wmap, wmap2, wmap3, P, grid, stream) : launch_t<B, false, MD>(xmap, wmap, wmap2, wmap3, P, grid, stream))
+    (bf ? launch_t<B, true, MD>(xmap, wmap, wmap2, wmap3, P, Q, grid, stream) : launch_t<B, false, MD>(xmap, wmap, wmap2, wmap3, P, Q, grid, stream))
 #define CB_WS_LAUNCH(B) (mode == 2 ? CB_WS_LAUNCH_M(B, 2) : mode == 1 ? CB_WS_LAUNCH_M(B, 1) : CB_WS_LAUNCH_M(B, 0))
     switch (bits) {
         case 2: return CB_WS_LAUNCH(2);
