@@ -340,7 +340,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         const int row = q * 32 + lane;                              // TMEM lane
         int n = (tile / P.tiles_m) * kOutCols + (GU ? (row >> 1) : row);
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-        bool nlive = n < P.N && (!GU || (lane & 1) == 0);            // fused gate/up: the gate lane stores
+        bool nlive = n < P.N;
         auto load_bias = [&](const __half* b, int r) {
             return b == nullptr ? 0.f
                    : BF ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(b)[r]) : __half2float(b[r]);
@@ -381,10 +381,16 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                          : "r"(taddr + (uint32_t)c0));
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             if constexpr (GU) {
+                // silu(gate) * up: the gate lane and the up lane of an output column share the work -- the gate lane
+                // finishes the even tokens of the chunk, the up lane the odd ones (one exchange per token pair);
+                // the result for token j + (lane & 1) is left in v[j], j even
+                const bool odd = (lane & 1) != 0;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {                       // silu(gate) * up: the up value sits in the next lane
-                    const float up = __shfl_xor_sync(0xffffffffu, __uint_as_float(v[j]), 1);
-                    v[j] = __float_as_uint(activate(__uint_as_float(v[j]), CB_ACT_SILU) * up);
+                for (int j = 0; j < 32; j += 2) {
+                    const float mine_even = __uint_as_float(v[j]), mine_odd = __uint_as_float(v[j + 1]);
+                    const float other = __shfl_xor_sync(0xffffffffu, odd ? mine_even : mine_odd, 1);
+                    const float gate = odd ? other : mine_even, up = odd ? mine_odd : other;
+                    v[j] = __float_as_uint(activate(gate, CB_ACT_SILU) * up);
                 }
             }
             if constexpr (QKV) {
@@ -406,12 +412,24 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             }
             if (nlive) {
                 __half* ocol = obase + (size_t)(m0 + c0) * ld + n;
+                if constexpr (GU) {
+                    const int odd = lane & 1;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    if (m0 + c0 + j < P.M) {
-                        const float y = (GU || QKV) ? __uint_as_float(v[j]) : activate(__uint_as_float(v[j]) + bias, P.act);
-                        if constexpr (BF) reinterpret_cast<__nv_bfloat16*>(ocol)[(size_t)j * ld] = __float2bfloat16_rn(y);
-                        else ocol[(size_t)j * ld] = __float2half_rn(y);
+                    for (int j = 0; j < 32; j += 2) {
+                        if (m0 + c0 + j + odd < P.M) {
+                            const float y = __uint_as_float(v[j]);
+                            if constexpr (BF) reinterpret_cast<__nv_bfloat16*>(ocol)[(size_t)(j + odd) * ld] = __float2bfloat16_rn(y);
+                            else ocol[(size_t)(j + odd) * ld] = __float2half_rn(y);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (m0 + c0 + j < P.M) {
+                            const float y = QKV ? __uint_as_float(v[j]) : activate(__uint_as_float(v[j]) + bias, P.act);
+                            if constexpr (BF) reinterpret_cast<__nv_bfloat16*>(ocol)[(size_t)j * ld] = __float2bfloat16_rn(y);
+                            else ocol[(size_t)j * ld] = __float2half_rn(y);
+                        }
                     }
                 }
             }
