@@ -617,6 +617,49 @@ def test_fused_qkv_prefill_outside_domain_falls_back():
     close(ov, ref_linear(x, vd, None), torch.float16, 3e-3)
 
 
+def test_prefill_kernels_on_seeded_random_shapes():
+    """Plain, fused gate/up and fused Q/K/V forms of the prefill kernel on 16 seeded random problems: token counts
+    around the 256-token tile edges, K from one super-block (128) up, head_dim 64 / 128, GQA widths, ragged gate/up
+    widths, fp16 and bf16, with and without bias and rotation; each against the fp32 reference."""
+    import random
+    from crispybits_kernels import _C, apply_rope_reference, fused_gate_up, packed_linear, permute_for_rope
+    rnd = random.Random(1)
+    for _ in range(16):
+        bits, dtype = rnd.choice([2, 3, 4]), rnd.choice([torch.float16, torch.bfloat16])
+        K, M = 128 * rnd.randint(1, 12), rnd.choice([129, 130, 255, 256, 257, 300, 511, 513, 777, 1025])
+        hd = rnd.choice([64, 128])
+        nq, nkv = rnd.randint(1, 6) * (128 // hd), rnd.randint(1, 3) * (128 // hd)
+        bias, rope = rnd.random() < 0.5, rnd.random() < 0.7
+        tol = 2e-2 if dtype == torch.bfloat16 else 3e-3
+        tag = (bits, dtype, M, K, hd, nq, nkv, bias, rope)
+        q, qd, qb = make(nq * hd, K, bits, dtype, DEV, bias, 1, 128, 0.02)
+        k, kd, kb = make(nkv * hd, K, bits, dtype, DEV, bias, 2, 128, 0.02)
+        v, vd, vb = make(nkv * hd, K, bits, dtype, DEV, bias, 3, 128, 0.02)
+        q, k = permute_for_rope(q, hd), permute_for_rope(k, hd)
+        x = torch.randn(M, K, device=DEV, dtype=dtype, generator=torch.Generator(DEV).manual_seed(M + K))
+        refs = [ref_linear(x, qd, qb), ref_linear(x, kd, kb), ref_linear(x, vd, vb)]
+        cos = sin = None
+        if rope:
+            cos, sin = rope_tables(M, hd, DEV)
+            refs[0], refs[1] = apply_rope_reference(refs[0], cos, sin, hd), apply_rope_reference(refs[1], cos, sin, hd)
+        e = torch.empty(0, device=DEV, dtype=dtype)
+        outs = _C.fused_qkv_gemm(x, q.packed, q.scales, q.zeros, q.bias if bias else e,
+                                 k.packed, k.scales, k.zeros, k.bias if bias else e,
+                                 v.packed, v.scales, v.zeros, v.bias if bias else e,
+                                 cos, sin, hd if rope else 0, hd, bits, K, 128)
+        assert outs is not None, tag
+        for o, r in zip(outs, refs):
+            assert rel_err(o, r) < tol, tag
+        n = rnd.choice([64, 100, 1000, 1376, 2048])
+        g, gd, _ = make(n, K, bits, dtype, DEV, False, 4, 128, 0.02)
+        u, ud, _ = make(n, K, bits, dtype, DEV, False, 5, 128, 0.02)
+        ref = torch.nn.functional.silu(x.float() @ gd.T) * (x.float() @ ud.T)
+        assert rel_err(fused_gate_up(x, g, u, decode_threshold=0), ref) < (2e-2 if dtype == torch.bfloat16 else 4e-3), tag
+        w, wd, wb = make(n - n % 8, K, bits, dtype, DEV, True, 6, 128, 0.02)
+        assert rel_err(packed_linear(x, w, act="silu", decode_threshold=0), ref_linear(x, wd, wb, "silu")) < tol, tag
+    assert _C.decode_status() == 0
+
+
 # ------------------------------------------------------------------ error behaviour
 def test_argument_errors():
     import crispybits_kernels as ck
