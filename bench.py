@@ -581,6 +581,46 @@ def reduce_sum(v):
     return _REDUCE_SUM[0](v) if _REDUCE_SUM[0] is not None else float(v)
 
 
+def _graph_timed_us(call, iters):
+    """Microseconds per call of `call(i)`: `iters` calls captured in one CUDA graph and replayed three times between
+    CUDA events (the host-side cost of a call -- Python, ctypes, tensor-map encoding -- is comparable to a 40 us
+    kernel and would otherwise be part of the figure); issued eagerly if the capture fails."""
+    for i in range(3):
+        call(i)
+    torch.cuda.synchronize()
+    replay = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            call(0)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                call(i)
+        replay = g.replay
+    except Exception as exc:
+        print(f"[bench] gemm graph capture failed: {type(exc).__name__}: {exc}", file=sys.stderr)
+        torch.cuda.synchronize()
+    reps = 3
+    if replay is not None:
+        replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        if replay is not None:
+            replay()
+        else:
+            for i in range(iters):
+                call(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (iters * reps)
+
+
 def bench_gemm(device, tf_peak, peak_kind, m=1024, iters=10):
     """Prefill GEMM at M=1024 (TFLOP/s = 2*M*N*K / t): the 4096x4096 matrix at W4 and W3, and at W4 the other
     three (N, K) shapes of the prefill configuration."""
@@ -589,16 +629,7 @@ def bench_gemm(device, tf_peak, peak_kind, m=1024, iters=10):
     for (n, k, b) in ((N_OUT, K_IN, 4), (N_OUT, K_IN, 3), (12288, 4096, 4), (22016, 4096, 4), (4096, 11008, 4)):
         x = torch.randn(m, k, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(5))
         ws = device_copies(synth_weight_numpy(b, b, n, k), device, 2)
-        for _ in range(3):
-            ck.packed_linear(x, ws[0])
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(iters):
-            ck.packed_linear(x, ws[i % 2])
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / iters
+        us = _graph_timed_us(lambda i: ck.packed_linear(x, ws[i % 2]), iters)
         tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
         out[f"m{m}_{n}x{k}_w{b}"] = {"us": us, "tflops": tf, "frac_of_dense_peak": tf / tf_peak,
                                      "peak_kind": f"of {peak_kind}"}
@@ -607,16 +638,7 @@ def bench_gemm(device, tf_peak, peak_kind, m=1024, iters=10):
     # the fused forms: gate/up (silu(g) * u in the epilogue) and Q/K/V (bias-free, RoPE and un-permuted stores in
     # the epilogue), both at K = 4096; FLOPs are those of the projections alone
     def timed(fn, flops):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / iters
+        us = _graph_timed_us(lambda i: fn(), iters)
         tf = flops / (us * 1e-6) / 1e12
         return {"us": us, "tflops": tf, "frac_of_dense_peak": tf / tf_peak, "peak_kind": f"of {peak_kind}"}
 
