@@ -839,10 +839,19 @@ int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_
     };
     int rc = encode_packed(&wmap, w);
     if (rc != CB_OK) return rc;
-    rc = encode_packed(&wmap2, gu ? w2 : qkv ? qkv->k : w);
-    if (rc != CB_OK) return rc;
-    rc = encode_packed(&wmap3, qkv ? qkv->v : w);
-    if (rc != CB_OK) return rc;
+    // maps the mode does not use are copies of the first (the kernel takes three): no further encoding on the host
+    if (gu || qkv != nullptr) {
+        rc = encode_packed(&wmap2, gu ? w2 : qkv->k);
+        if (rc != CB_OK) return rc;
+    } else {
+        wmap2 = wmap;
+    }
+    if (qkv != nullptr) {
+        rc = encode_packed(&wmap3, qkv->v);
+        if (rc != CB_OK) return rc;
+    } else {
+        wmap3 = wmap;
+    }
 
     GemmParams P{};
     QkvParams Q{};
