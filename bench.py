@@ -1,16 +1,22 @@
 #!/usr/bin/env python3
 """Benchmark of the packed W2/W3/W4 linear path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload gemv|stack]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Prints ONE JSON line.  Workload at N=1 (`gemv`): batch-1 decode GEMVs over 4096x4096 group-128 weights
-at W4, W3 and W2 -- the shapes the headline metric is quoted on.  A step is one pass over COPIES
+Prints ONE JSON line.  Top-level workload at every N: batch-1 decode GEMVs over 4096x4096 group-128 weights
+at W4, W3 and W2 -- the shapes the headline metric is quoted on; at N > 1 every rank runs its own replica
+(single matmuls stay on one GPU, so the top-level figure scales weakly and has no collective).  The path that
+shards -- the 32-block decode stack, column-parallel over the N GPUs -- is the `stack` object of the same
+line at every N, with its own correctness check, the 1-GPU time measured in the same run, and the speed-up.
+Further objects: `gemv_sweep` (bit-width x shape x batch sweep of the decode GEMV), `fused_decode` (fused
+QKV / gate-up at batch 1, API form and concatenated form), `gemm` (prefill GEMM sweep).  A step is one pass over COPIES
 distinct weight matrices per bit-width (3*COPIES launches); the matrices of one step add up to more
 than twice the 126 MB L2, so every launch streams its weights from HBM.  `value` is the algorithmic
 bytes of all launches divided by the device time of the timed steps (CUDA events on the launching
 stream around CUDA-graph replays of a step, so Python launch overhead is not in the number).  `e2e`
 times the same GEMVs through the public API with the activations starting in pinned host memory and
-the result read back to the host every call.  `roofline` describes the dominant kernel (the W4 GEMV):
+the result read back to the host every call; its `value` is the step captured on ONE stream (what a caller of
+packed_linear gets), the multi-stream and eager variants are reported beside it.  `roofline` describes the dominant kernel (the W4 GEMV):
 algorithmic bytes per launch over its average launch duration, against the measured HBM copy
 bandwidth in MEASURED_PEAKS.json.  `cpu_baseline` is the C oracle (OpenMP, all host threads) timed on
 a bounded sample of the same GEMVs on the host cores.
@@ -44,7 +50,7 @@ N_OUT, K_IN, GROUP = 4096, 4096, 128
 BITS = (4, 3, 2)
 COPIES = 48                 # distinct weight matrices per bit-width and step (about 1 GB in all)
 E2E_STREAMS = 5             # streams the end-to-end step is pipelined over
-FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+FALLBACK_HBM_GBS = 6650.0   # used only without MEASURED_PEAKS.json
 FALLBACK_TFLOPS = 1590.0
 METRIC = "packed W2/3/4 decode GEMV effective HBM bandwidth (4096x4096, group 128, batch 1)"
 COMM_TEXT = {
@@ -55,7 +61,10 @@ COMM_TEXT = {
 }
 METRIC_STACK = "packed mixed-precision decode stack effective HBM bandwidth (Llama-2-7B shapes, 32 blocks)"
 # dram__bytes_read + dram__bytes_write per W4 4096x4096 launch, from the ncu capture summarised under profiles/
-NCU_TRAFFIC_W4 = 8958464
+# (profiles/gemv_stream_w4_4096x4096_b1.md: the ring kernel's loads are one bulk copy per packed row plus the
+# scales and zeros, each byte once)
+NCU_TRAFFIC_W4 = 8977664
+L2_BYTES = 126e6
 
 
 def gemv_bytes(n, k, bits, batch=1, group=GROUP):
@@ -188,7 +197,7 @@ def cpu_gemv_sample(seconds_per_bits=3.0, min_iters=3, copies=2):
     """Time the C oracle's decode GEMV (OpenMP over output rows, all host threads) on the benchmark's
     three 4096x4096 matrices.  Returns (GB/s over the sample, per-bits ms, threads, description)."""
     from oracle import cb_oracle_c as OC
-    threads = OC.num_threads()
+    threads = OC.use_all_host_threads()        # a launcher may have exported OMP_NUM_THREADS=1
     g = torch.Generator().manual_seed(123)
     x = torch.randn(1, K_IN, generator=g).half().float().numpy()
     total_bytes, total_s, per = 0, 0.0, {}
@@ -226,7 +235,7 @@ def run_reference_arm(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "gemv_4096x4096_w4_w3_w2_b1", "group_size": GROUP,
                    "note": "CPU implementation of the reference's decode arithmetic on the host cores"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
@@ -310,7 +319,7 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
         us = ms * 1e3 / (args.steps * COPIES)
         gbs = gemv_bytes(N_OUT, K_IN, b) / (us * 1e-6) / 1e9
         gemv[f"w{b}"] = {"us": us, "gbs": gbs, "frac_of_hbm_peak": gbs / hbm_peak,
-                         "split_k": ops._resolve(None, 1, 1, N_OUT, K_IN, torch.device(device))}
+                         "split_k": ops._resolve(None, 1, 1, N_OUT, K_IN, torch.device(device), torch.float16, GROUP)}
     top = gemv["w4"]
     roofline = {"bound": "hbm", "achieved": top["gbs"], "peak": hbm_peak, "unit": "GB/s",
                 "frac": top["gbs"] / hbm_peak, "traffic": NCU_TRAFFIC_W4, "kernel": "decode GEMV W4 4096x4096 b1",
@@ -416,7 +425,9 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
         except Exception as exc:
             print(f"[bench] pipelined e2e capture failed: {type(exc).__name__}: {exc}", file=sys.stderr)
             torch.cuda.synchronize()
-    e2e_ms = min(m for m in (piped_ms, graph_ms, eager_ms) if m is not None)
+    # The headline is what a caller of packed_linear gets on its stream: the one-stream captured step (the eager
+    # figure if capture is not available).  The multi-stream pipelined step is reported beside it.
+    e2e_ms = graph_ms if graph_ms is not None else eager_ms
     gbs = lambda ms: world * step_bytes * args.steps / (ms * 1e-3) / 1e9
     e2e = {"value": gbs(e2e_ms), "unit": "GB/s",
            "h2d_bytes_per_step": 3 * COPIES * K_IN * 2, "d2h_bytes_per_step": 3 * COPIES * N_OUT * 2,
@@ -424,15 +435,16 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
            "one_stream_graph_value": None if graph_ms is None else gbs(graph_ms),
            "pipelined_graph_value": None if piped_ms is None else gbs(piped_ms),
            "api": "crispybits_kernels.packed_linear; per call x is copied from pinned host memory and y copied back to "
-                  "pinned host memory; packed weights resident on the device as in install_bitmap; "
-                  + (f"the step's calls and copies are captured in a CUDA graph over {E2E_STREAMS} streams (the calls "
-                     "of a step are independent, so the copies of one overlap the kernels of others) and replayed "
-                     "(one_stream_graph_value: the same step captured on one stream; eager_value: issued call by call "
-                     "from Python)" if piped_ms is not None and piped_ms <= e2e_ms else
-                     "the step's calls and copies are captured in a CUDA graph and replayed (eager_value: the same "
-                     "step issued call by call from Python)" if graph_ms is not None else "issued call by call from Python")}
+                  "pinned host memory; packed weights resident on the device as in install_bitmap; value: the step's "
+                  "calls and copies captured on one stream in a CUDA graph and replayed; eager_value: the same step "
+                  f"issued call by call from Python; pipelined_graph_value: the same step captured over {E2E_STREAMS} "
+                  "streams (the calls of this benchmark step are independent, so the copies of one overlap the kernels "
+                  "of others; a decode step's calls are not)"}
 
     extra = {}
+    if rank == 0 and not args.no_sweeps:
+        extra["gemv_sweep"] = bench_gemv_sweep(device, hbm_peak, peak_kind)
+        extra["fused_decode"] = bench_fused_decode(device, hbm_peak, peak_kind)
     if rank == 0 and not args.no_gemm:
         extra["gemm"] = bench_gemm(device, tf_peak, peak_kind)
     cpu = None
@@ -443,10 +455,11 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
     return {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "gemv_4096x4096_w4_w3_w2_b1", "group_size": GROUP, "copies_per_bits": COPIES,
                    "l2": f"inputs larger than L2: each step streams {step_bytes / 1e6:.0f} MB of distinct weights "
-                         f"(126 MB L2)", "launch": "CUDA graph replay, one graph per bit-width",
+                         f"(126 MB L2)", "launch": "CUDA graph replay, one graph per bit-width; the calls of a graph "
+                         "read the same x and write their own outputs",
                    "multi_gpu": "independent replicas (single matmuls stay on one GPU)" if world > 1 else "n/a"},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gemv": gemv, "clocks": clocks,
         "gpu_launches": args.steps * 3 * COPIES, **extra,
@@ -454,45 +467,56 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
 
 
 # ------------------------------------------------------------------ GPU arm: decode stack workload
-def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False):
-    """One step = the 128 packed decode launches of a Llama-2-7B-shaped 32-block stack (per-block bit-widths
-    from the seeded {2,3,4} draw), column-parallel over `world` GPUs with an all-gather after each launch."""
-    import crispybits_kernels as ck
-    from crispybits_kernels.stack import DecodeStack
-    hbm_peak, _, peak_kind = peaks()
-    batch = args.batch
-    st = DecodeStack(rank=rank, world=world, device=device, comm=args.comm)
-    g = torch.Generator().manual_seed(2)
-    x_host = torch.randn(batch, st.d_model, generator=g).half().pin_memory()
-    x = x_host.to(device)
-    comm_note = None
-    try:
-        for _ in range(2):
-            y = st.step(x)
-        torch.cuda.synchronize()
-        ok = 1.0
-    except Exception as exc:      # e.g. peer-mapped memory cannot be set up on this box
-        comm_note = f"{type(exc).__name__}: {exc}"[:200]
-        ok = 0.0
+def _stack_parity(args, rank, world, device, comm):
+    """A 3-block stack of the same shapes, sharded like the timed one: (1) with more than one rank the requested gather
+    must give bit for bit what the NCCL gather gives; (2) the result must match the fp32 evaluation of the same data
+    flow from the full (un-sharded) weights, which rank 0 rebuilds with the library's unpack kernel.  Returns the
+    maximum relative error of (2) on rank 0."""
+    import torch.distributed as dist
+    from crispybits_kernels import _C
+    from crispybits_kernels.stack import DecodeStack, sample_bitmap
+    bm = sample_bitmap(32, 0)[:3]
+    x = torch.randn(args.batch, 4096, generator=torch.Generator().manual_seed(11)).half().to(device)
+    st = DecodeStack(n_blocks=3, bitmap=bm, rank=rank, world=world, device=device, comm=comm)
+    y = st.step(x).clone()
+    torch.cuda.synchronize()
     if world > 1 and st.comm != "nccl":
-        # every rank must take the same path: if the peer-memory set-up failed anywhere, all ranks use NCCL, and the
-        # line says so
-        all_ok = -reduce_max(-ok)
-        if all_ok < 1.0:
-            print(f"[bench] rank {rank}: peer-store gather unavailable ({comm_note}); using the NCCL gather", file=sys.stderr)
-            st.comm = "nccl"
-            comm_note = comm_note or "peer set-up failed on another rank"
-            for _ in range(2):
-                y = st.step(x)
-            torch.cuda.synchronize()
-        else:
-            comm_note = None
-    elif ok < 1.0:
-        raise RuntimeError(comm_note)
-    assert torch.isfinite(y.float()).all(), "decode stack produced non-finite values"
+        requested, st.comm = st.comm, "nccl"
+        y_nccl = st.step(x).clone()
+        st.comm = requested
+        torch.cuda.synchronize()
+        if not torch.equal(y, y_nccl):
+            raise RuntimeError(f"rank {rank}: the {requested} gather and the NCCL gather disagree")
+    err = 0.0
+    if rank == 0:
+        one = DecodeStack(n_blocks=3, bitmap=bm, rank=0, world=1, device=device) if world > 1 else st
+        full = []
+        for blk in one.blocks:
+            dq = {}
+            for name in ("q", "k", "v", "o", "gate", "up", "down"):
+                w = getattr(blk, name)
+                codes = _C.unpack_codes(w.packed.contiguous(), w.bits, w.in_features).float()
+                sc = w.scales.float().repeat_interleave(w.group_size, 1)[:, :w.in_features]
+                zc = w.zeros.float().repeat_interleave(w.group_size, 1)[:, :w.in_features]
+                dq[name] = (codes - zc) * sc
+            full.append(dq)
+        ref = one.reference_step(x, full)
+        err = float((y.float() - ref).abs().max() / ref.abs().max())
+        if not err < 4e-3:              # four chained fp16 launches per block
+            raise RuntimeError(f"decode stack off by {err:.2e} against the fp32 data flow; not timing")
+        del one, full
+    del st
+    torch.cuda.empty_cache()
+    if world > 1:
+        dist.barrier()
+    return err
+
+
+def _time_stack(st, x, args, barrier, reduce_max):
+    """ms per step (device time, max over ranks), the graph or eager callable that was timed, and how it was launched."""
     graph, mode = None, "eager launches"
     try:
-        side = torch.cuda.Stream(device)
+        side = torch.cuda.Stream(x.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             st.step(x)
@@ -508,6 +532,7 @@ def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False
         graph = None
         mode = f"eager launches (graph capture failed: {type(exc).__name__})"
         torch.cuda.synchronize()
+        y = st.step(x)
 
     def one_step():
         if graph is not None:
@@ -515,12 +540,8 @@ def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False
         else:
             st.step(x)
 
-    warm = max(3, args.warmup)
-    for _ in range(warm):
+    for _ in range(max(3, args.warmup)):
         one_step()
-    sampler = ClockSampler(torch.cuda.current_device())
-    if rank == 0 and not sub:
-        sampler.start()
     barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -530,12 +551,43 @@ def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False
     e1.record()
     torch.cuda.synchronize()
     barrier()
-    clocks = sampler.stop() if (rank == 0 and not sub) else {}
-    total_ms = reduce_max(e0.elapsed_time(e1))
+    return reduce_max(e0.elapsed_time(e1)) / args.steps, one_step, y, mode
+
+
+def run_stack_workload(args, rank, world, device, barrier, reduce_max):
+    """One step = the 128 packed decode launches of a Llama-2-7B-shaped 32-block stack (per-block bit-widths
+    from the seeded {2,3,4} draw), column-parallel over `world` GPUs with a gather after each launch."""
+    from crispybits_kernels.stack import DecodeStack
+    hbm_peak, _, peak_kind = peaks()
+    batch = args.batch
+    st = DecodeStack(rank=rank, world=world, device=device, comm=args.comm)
+    x_host = torch.randn(batch, st.d_model, generator=torch.Generator().manual_seed(2)).half().pin_memory()
+    x = x_host.to(device)
+    comm_note = None
+    try:
+        for _ in range(2):
+            st.step(x)
+        torch.cuda.synchronize()
+        ok = 1.0
+    except Exception as exc:      # e.g. peer-mapped memory cannot be set up on this box
+        comm_note = f"{type(exc).__name__}: {exc}"[:200]
+        ok = 0.0
+    if world > 1 and st.comm != "nccl":
+        # every rank must take the same path: if the peer-memory set-up failed anywhere, all ranks use NCCL
+        if -reduce_max(-ok) < 1.0:
+            print(f"[bench] rank {rank}: peer-store gather unavailable ({comm_note}); using the NCCL gather", file=sys.stderr)
+            st.comm = "nccl"
+            comm_note = comm_note or "peer set-up failed on another rank"
+        else:
+            comm_note = None
+    elif ok < 1.0:
+        raise RuntimeError(comm_note)
+    parity_err = _stack_parity(args, rank, world, device, st.comm)
+
+    ms, one_step, y, mode = _time_stack(st, x, args, barrier, reduce_max)
     my_bytes = st.algorithmic_bytes(batch)
     all_bytes = reduce_sum(float(my_bytes)) if world > 1 else float(my_bytes)
-    value = all_bytes * args.steps / (total_ms * 1e-3) / 1e9
-
+    value = all_bytes / (ms * 1e-3) / 1e9
     if st.peer_status() != 0:
         raise RuntimeError(f"rank {rank}: peer {st.peer_status() - 1} was not heard from in time")
     y_host = torch.empty(batch, st.d_model, dtype=torch.float16).pin_memory()
@@ -552,25 +604,39 @@ def run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=False
     t0 = time.perf_counter()
     for _ in range(args.steps):
         e2e_step()
-    e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3)
+    e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3) / args.steps
+    launches, comm_used, bitmap = st.launches_per_step(), st.comm, list(st.bitmap)
+    del st, one_step, y
+    torch.cuda.empty_cache()
+
+    # the same step on ONE GPU, timed in this run on rank 0 (at N = 1 that is the figure above)
+    single_ms = ms
+    if world > 1:
+        if rank == 0:
+            one = DecodeStack(rank=0, world=1, device=device)
+            single_ms = _time_stack(one, x, args, lambda: None, float)[0]
+            del one
+            torch.cuda.empty_cache()
+        barrier()
     res = {
-        "metric": METRIC_STACK, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
-        "ms_per_step": total_ms / args.steps, "us_per_launch": total_ms * 1e3 / args.steps / st.launches_per_step(),
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "metric": METRIC_STACK, "value": value, "unit": "GB/s", "n_gpus": world, "ms_per_step": ms,
+        "us_per_launch": ms * 1e3 / (4 * 32), "scaling": "strong",
+        "single_gpu_ms_per_step": single_ms, "speedup_vs_1gpu": single_ms / ms,
+        "parity_checked": True, "parity_max_rel_err_vs_fp32_dataflow": parity_err,
+        "parity_note": "3-block stack of the same shapes before timing: " + ("requested gather == NCCL gather bit for bit on every rank; " if world > 1 and comm_used != "nccl" else "")
+                       + "rank 0 against the fp32 evaluation of the data flow from the full weights (bound 4e-3)",
         "config": {"workload": "decode_stack_llama2_7b_32blocks", "batch": batch, "bitmap_seed": 0,
-                   "mean_bits": float(np.mean(st.bitmap)), "parallelism": (f"column-parallel N over {world} GPUs, " + COMM_TEXT[st.comm]
+                   "mean_bits": float(np.mean(bitmap)), "parallelism": (f"column-parallel N over {world} GPUs, " + COMM_TEXT[comm_used]
                                    + (f" [requested {args.comm}: {comm_note}]" if comm_note else "")) if world > 1 else "single GPU",
                    "l2": f"inputs larger than L2: {my_bytes / 1e6:.0f} MB of weights per rank and step", "launch": mode},
         "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
                      "frac": value / world / hbm_peak, "traffic": None, "kernel": "decode step, per GPU",
-                     "algorithmic_bytes_per_launch": my_bytes / st.launches_per_step(), "peak_kind": f"of {peak_kind}"},
-        "e2e": {"value": all_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-                "h2d_bytes_per_step": batch * st.d_model * 2, "d2h_bytes_per_step": batch * st.d_model * 2,
+                     "algorithmic_bytes_per_launch": my_bytes / (4 * 32), "peak_kind": f"of {peak_kind}"},
+        "e2e": {"value": all_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": batch * 4096 * 2, "d2h_bytes_per_step": batch * 4096 * 2,
                 "api": "DecodeStack.step: hidden state from pinned host memory, result copied back, every step"},
-        "cpu_baseline": None, "clocks": clocks, "gpu_launches": args.steps * st.launches_per_step(),
+        "gpu_launches_per_step": launches,
     }
-    del st
-    torch.cuda.empty_cache()
     return res
 
 
@@ -621,40 +687,159 @@ def _graph_timed_us(call, iters):
     return e0.elapsed_time(e1) * 1e3 / (iters * reps)
 
 
-def bench_gemm(device, tf_peak, peak_kind, m=1024, iters=10):
-    """Prefill GEMM at M=1024 (TFLOP/s = 2*M*N*K / t): the 4096x4096 matrix at W4 and W3, and at W4 the other
-    three (N, K) shapes of the prefill configuration."""
+def _oracle_dequant(d):
+    """fp32 [N, K] weight the packed dictionary stands for, by the C oracle (the check value of the gates below)."""
+    from oracle import cb_oracle_c as OC
+    return OC.dequantized_weight(d["packed"], d["scales"], d["zeros"], d["bits"], d["in_features"], GROUP)
+
+
+def _gate(name, y, ref, tol=2e-3):
+    err = float((y.float() - ref).abs().max() / ref.abs().max())
+    if not err < tol:
+        raise RuntimeError(f"{name}: off by {err:.2e} against the oracle's dequantised weight; not timing")
+    return err
+
+
+def _copies_beyond_l2(nbytes, floor=2):
+    return max(floor, int(np.ceil(2.2 * L2_BYTES / nbytes)))
+
+
+SWEEP_SHAPES = ((4096, 4096), (11008, 4096), (4096, 11008))
+
+
+def bench_gemv_sweep(device, hbm_peak, peak_kind, iters_per_graph=1):
+    """Decode GEMV over bits {2,3,4} x (N,K) in {(4096,4096), (11008,4096), (4096,11008)} x batch {1,2,4,8}: us per
+    launch, algorithmic GB/s and fraction of the HBM peak.  Each case walks enough distinct matrices to exceed twice
+    the L2 (so every launch streams from HBM), captured back to back in one CUDA graph; each (bits, shape) is first
+    checked against the oracle's dequantised weight for every batch size."""
     import crispybits_kernels as ck
     out = {}
-    for (n, k, b) in ((N_OUT, K_IN, 4), (N_OUT, K_IN, 3), (12288, 4096, 4), (22016, 4096, 4), (4096, 11008, 4)):
-        x = torch.randn(m, k, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(5))
-        ws = device_copies(synth_weight_numpy(b, b, n, k), device, 2)
-        us = _graph_timed_us(lambda i: ck.packed_linear(x, ws[i % 2]), iters)
-        tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
-        out[f"m{m}_{n}x{k}_w{b}"] = {"us": us, "tflops": tf, "frac_of_dense_peak": tf / tf_peak,
-                                     "peak_kind": f"of {peak_kind}"}
-        del ws, x
+    for (n, k) in SWEEP_SHAPES:
+        for b in BITS:
+            d = synth_weight_numpy(b, 40 + b, n, k)
+            ws = device_copies(d, device, _copies_beyond_l2(gemv_bytes(n, k, b)))
+            wd = torch.from_numpy(_oracle_dequant(d)).to(device)
+            for batch in (1, 2, 4, 8):
+                x = torch.randn(batch, k, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(batch))
+                err = _gate(f"gemv w{b} {n}x{k} b{batch}", ck.packed_linear(x, ws[0], decode_threshold=8), x.float() @ wd.T)
+                us = _graph_timed_us(lambda i: ck.packed_linear(x, ws[i % len(ws)], decode_threshold=8), len(ws))
+                gbs = gemv_bytes(n, k, b, batch) / (us * 1e-6) / 1e9
+                out[f"w{b}_{n}x{k}_b{batch}"] = {"us": round(us, 3), "gbs": round(gbs, 1), "frac": round(gbs / hbm_peak, 4),
+                                                 "err": float(f"{err:.2e}")}
+            del ws, wd
+            torch.cuda.empty_cache()
+    out["note"] = (f"fraction of the HBM copy peak {hbm_peak:.0f} GB/s ({peak_kind}); L2-cold: each graph walks more "
+                   "than twice the L2 of distinct matrices; err = max relative error against the oracle")
+    return out
 
-    # the fused forms: gate/up (silu(g) * u in the epilogue) and Q/K/V (bias-free, RoPE and un-permuted stores in
-    # the epilogue), both at K = 4096; FLOPs are those of the projections alone
+
+def bench_fused_decode(device, hbm_peak, peak_kind):
+    """W3, batch 1: the fused Q/K/V and gate/up decode launches in the API's form (three / two weights, three / one
+    outputs) and as one GEMV over the row-concatenated matrix."""
+    import crispybits_kernels as ck
+    from crispybits_kernels import PackedLinearWeight
+    out, b, k = {}, 3, 4096
+    x = torch.randn(1, k, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(3))
+
+    def cat(ws):
+        return PackedLinearWeight(torch.cat([w.packed for w in ws]), torch.cat([w.scales for w in ws]),
+                                  torch.cat([w.zeros for w in ws]), b, GROUP, k, sum(w.out_features for w in ws))
+
+    def entry(us, nbytes):
+        gbs = nbytes / (us * 1e-6) / 1e9
+        return {"us": round(us, 3), "gbs": round(gbs, 1), "frac": round(gbs / hbm_peak, 4)}
+
+    # Q/K/V: 3 x (4096, 4096), seeds 1, 2, 3
+    dq = [synth_weight_numpy(b, s, 4096, k) for s in (1, 2, 3)]
+    ncopy = _copies_beyond_l2(3 * gemv_bytes(4096, k, b))
+    sets = list(zip(*[device_copies(d, device, ncopy) for d in dq]))
+    refs = [x.float() @ torch.from_numpy(_oracle_dequant(d)).to(device).T for d in dq]
+    for o, r, nm in zip(ck.fused_qkv(x, *sets[0]), refs, "qkv"):
+        _gate(f"fused_qkv {nm}", o, r)
+    nbytes = gemv_bytes(12288, k, b)
+    out["qkv_12288x4096_w3_fused_api"] = entry(_graph_timed_us(lambda i: ck.fused_qkv(x, *sets[i % ncopy]), ncopy), nbytes)
+    cats = [cat(st) for st in sets]
+    _gate("concatenated qkv", ck.packed_linear(x, cats[0]), torch.cat(refs, 1))
+    out["qkv_12288x4096_w3_concatenated"] = entry(_graph_timed_us(lambda i: ck.packed_linear(x, cats[i % ncopy]), ncopy), nbytes)
+    del sets, cats, refs
+    torch.cuda.empty_cache()
+    # gate/up: 2 x (11008, 4096), seeds 5, 6
+    dg = [synth_weight_numpy(b, s, 11008, k) for s in (5, 6)]
+    ncopy = _copies_beyond_l2(2 * gemv_bytes(11008, k, b))
+    sets = list(zip(*[device_copies(d, device, ncopy) for d in dg]))
+    rg, ru = (x.float() @ torch.from_numpy(_oracle_dequant(d)).to(device).T for d in dg)
+    _gate("fused_gate_up", ck.fused_gate_up(x, *sets[0]), torch.nn.functional.silu(rg) * ru)
+    out["gate_up_2x11008x4096_w3_fused_api"] = entry(_graph_timed_us(lambda i: ck.fused_gate_up(x, *sets[i % ncopy]), ncopy),
+                                                     2 * gemv_bytes(11008, k, b) - k * 2 - 11008 * 2)
+    cats = [cat(st) for st in sets]
+    _gate("concatenated gate/up", ck.packed_linear(x, cats[0]), torch.cat([rg, ru], 1))
+    out["gate_up_22016x4096_w3_concatenated"] = entry(_graph_timed_us(lambda i: ck.packed_linear(x, cats[i % ncopy]), ncopy),
+                                                      gemv_bytes(22016, k, b))
+    out["note"] = f"fraction of the HBM copy peak {hbm_peak:.0f} GB/s ({peak_kind}); L2-cold as the sweep"
+    return out
+
+
+GEMM_SHAPES = ((4096, 4096), (12288, 4096), (22016, 4096), (4096, 11008))
+GEMM_TOKENS = (128, 512, 1024, 4096)
+
+
+def bench_gemm(device, tf_peak, peak_kind, iters=10):
+    """Prefill GEMM (TFLOP/s = 2*M*N*K / t) for W4 and W3, M in {128, 512, 1024, 4096}, the four Llama-2-7B (N, K)
+    shapes, plus the fused gate/up and Q/K/V forms at M = 1024.  Every figure is preceded by a check of the same
+    call against the fp32 product with the oracle's dequantised weight (2e-3)."""
+    import crispybits_kernels as ck
+    out = {}
+    for (n, k) in GEMM_SHAPES:
+        for b in (4, 3):
+            d = synth_weight_numpy(b, 60 + b, n, k)
+            ws = device_copies(d, device, 2)
+            wd = torch.from_numpy(_oracle_dequant(d)).to(device)
+            for m in GEMM_TOKENS:
+                x = torch.randn(m, k, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(5 + m))
+                y = ck.packed_linear(x, ws[0])
+                rows = min(m, 512)                 # the check covers the first 512 tokens of the call (every weight row)
+                err = _gate(f"gemm w{b} m{m} {n}x{k}", y[:rows], x[:rows].float() @ wd.T)
+                us = _graph_timed_us(lambda i: ck.packed_linear(x, ws[i % 2]), iters if m <= 1024 else 4)
+                tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
+                out[f"m{m}_{n}x{k}_w{b}"] = {"us": round(us, 2), "tflops": round(tf, 1), "frac_of_dense_peak": round(tf / tf_peak, 4),
+                                             "err": float(f"{err:.2e}")}
+                del x, y
+            del ws, wd
+            torch.cuda.empty_cache()
+
+    # the fused forms at M = 1024, K = 4096: gate/up (silu(g) * u in the epilogue) and Q/K/V (RoPE and un-permuted
+    # stores in the epilogue); FLOPs are those of the projections alone
     def timed(fn, flops):
         us = _graph_timed_us(lambda i: fn(), iters)
         tf = flops / (us * 1e-6) / 1e12
-        return {"us": us, "tflops": tf, "frac_of_dense_peak": tf / tf_peak, "peak_kind": f"of {peak_kind}"}
+        return {"us": round(us, 2), "tflops": round(tf, 1), "frac_of_dense_peak": round(tf / tf_peak, 4)}
 
-    k, hd = 4096, 128
+    m, k, hd = 1024, 4096, 128
     x = torch.randn(m, k, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(6))
-    gate = device_copies(synth_weight_numpy(4, 11, 11008, k), device, 1)[0]
-    up = device_copies(synth_weight_numpy(4, 12, 11008, k), device, 1)[0]
+    dgs = [synth_weight_numpy(4, s, 11008, k) for s in (11, 12)]
+    gate, up = (device_copies(d, device, 1)[0] for d in dgs)
+    rg, ru = (x[:256].float() @ torch.from_numpy(_oracle_dequant(d)).to(device).T for d in dgs)
+    _gate("fused gate/up gemm", ck.fused_gate_up(x, gate, up)[:256], torch.nn.functional.silu(rg) * ru, 3e-3)
     out[f"m{m}_gate_up_11008x{k}_w4"] = timed(lambda: ck.fused_gate_up(x, gate, up), 2.0 * m * 2 * 11008 * k)
-    del gate, up
-    q, kk, v = (device_copies(synth_weight_numpy(4, 13 + i, 4096, k), device, 1)[0] for i in range(3))
-    q, kk = ck.permute_for_rope(q, hd), ck.permute_for_rope(kk, hd)
+    del gate, up, rg, ru
+    dqs = [synth_weight_numpy(4, 13 + i, 4096, k) for i in range(3)]
+    q, kk, v = (device_copies(d, device, 1)[0] for d in dqs)
+    plain = ck.fused_qkv(x, q, kk, v)
+    for o, d, nm in zip(plain, dqs, "qkv"):
+        _gate(f"fused qkv gemm {nm}", o[:256], x[:256].float() @ torch.from_numpy(_oracle_dequant(d)).to(device).T)
+    from crispybits_kernels.ops import apply_rope_reference as ops_rope
+    qp, kp = ck.permute_for_rope(q, hd), ck.permute_for_rope(kk, hd)
     pos = torch.arange(m, device=device, dtype=torch.float32)[:, None]
     inv = 10000.0 ** (-torch.arange(0, hd, 2, device=device, dtype=torch.float32) / hd)
     ang = torch.cat([pos * inv, pos * inv], dim=1)
     rope = (ang.cos().contiguous(), ang.sin().contiguous(), hd)
-    out[f"m{m}_qkv_rope_12288x{k}_w4"] = timed(lambda: ck.fused_qkv(x, q, kk, v, rope=rope), 2.0 * m * 12288 * k)
+    roped = ck.fused_qkv(x, qp, kp, v, rope=rope)
+    for o, base, nm in zip(roped[:2], plain[:2], "qk"):      # rotation of the checked plain result, in fp32
+        want = ops_rope(base.float(), rope[0], rope[1], hd)
+        _gate(f"fused qkv gemm rope {nm}", o, want.float(), 4e-3)
+    out[f"m{m}_qkv_rope_12288x{k}_w4"] = timed(lambda: ck.fused_qkv(x, qp, kp, v, rope=rope), 2.0 * m * 12288 * k)
+    out["note"] = (f"fraction of the dense tensor peak {tf_peak:.0f} TFLOP/s (cuBLAS bf16, {peak_kind}); graph replay of "
+                   "back-to-back calls; err = max relative error against the oracle's dequantised weight")
     return out
 
 
@@ -664,10 +849,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "gemv", "stack"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM figures")
-    ap.add_argument("--no-stack", action="store_true", help="skip the 1-GPU decode-stack figures at N=1")
+    ap.add_argument("--no-sweeps", action="store_true", help="skip the decode sweep and the fused decode figures")
+    ap.add_argument("--no-stack", action="store_true", help="skip the decode-stack figures")
     ap.add_argument("--comm", default="p2p_barrier", choices=["nccl", "p2p", "p2p_barrier"],
                     help="how the column-parallel stack gathers its activations at N > 1")
     ap.add_argument("--batch", type=int, default=1, help="decode batch of the stack workload (1..8)")
@@ -709,17 +894,12 @@ def main():
         return float(t.item())
 
     _REDUCE_SUM[0] = reduce_sum_impl
-    # N = 1: the 4096x4096 GEMVs the headline metric is quoted on (plus, as extra objects, the prefill GEMM
-    # and the 1-GPU decode stack).  N > 1: single matmuls stay on one GPU, so the path that shards -- the
-    # decode stack -- is what runs; the "stack" object of the N = 1 line is its 1-GPU point.
-    workload = args.workload or ("gemv" if world == 1 else "stack")
-    if workload == "stack":
-        line = run_stack_workload(args, rank, world, device, barrier, reduce_max)
-    else:
-        line = run_gemv_workload(args, rank, world, device, barrier, reduce_max)
-        if world == 1 and not args.no_stack:
-            sub = run_stack_workload(args, rank, world, device, barrier, reduce_max, sub=True)
-            line["stack"] = {k: sub[k] for k in ("metric", "value", "unit", "ms_per_step", "us_per_launch", "config", "roofline", "e2e")}
+    # Top level at every N: the 4096x4096 GEMVs the headline metric is quoted on, one replica per rank (single
+    # matmuls stay on one GPU).  The path that shards -- the decode stack -- is the "stack" object at every N.
+    line = run_gemv_workload(args, rank, world, device, barrier, reduce_max)
+    if not args.no_stack:
+        line["stack"] = run_stack_workload(args, rank, world, device, barrier, reduce_max)
+        line["gpu_launches"] += args.steps * line["stack"]["gpu_launches_per_step"]
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:

@@ -192,7 +192,8 @@ int cb_quantize_pack(const void* w, int w_dtype, int64_t n, int64_t K, int bits,
  *   - split_k * B * n must not exceed 262144 (the array's partial-sum room) and
  *     ceil(B/8) * ceil(n/16) must not exceed 65536; larger requests fail with CB_ERR_INVALID;
  *   - the first call on each device looks up the array's device address; make that first call
- *     outside any stream capture;
+ *     outside any stream capture.  The address is kept for the life of the process, so the entry
+ *     point must not be used on a device after cudaDeviceReset() of that device;
  *   - all calls on a device share the one array: calls that can overlap on the GPU (different
  *     streams, or graphs replayed concurrently) race on it -- serialise them, or give the
  *     overlapping ones their own buffers through cb_packed_gemv. */
@@ -212,13 +213,30 @@ size_t cb_gemv_scratch_bytes(int64_t B, int64_t V, int64_t split_k);
  * streamlined decode kernel, value 0/1 (default 1, or 0 when CRISPYBITS_PDL=0 is in the environment).
  * With it on, a decode call may start fetching PACKED WEIGHTS before the previous kernel of the
  * stream has finished; activations, outputs and scratch are only touched afterwards.  option 1:
- * value 1 forces the shape-generic decode kernel everywhere (for A/B checks).  option 2: which
- * fp16 decode kernel runs where both apply -- 0 (default) and 1 the shared-memory ring kernel, 2 the
- * register-streaming kernel (faster for an isolated large matrix at batch 1-2, slower inside a chain of
- * dependent launches).  option 3: which tcgen05 prefill kernel -- 0 (default) by M, 1 the kernel with both
+ * value 1 forces the shape-generic decode kernel everywhere (for A/B checks).  option 2: unused.  option 3: which tcgen05 prefill kernel -- 0 (default) by M, 1 the kernel with both
  * operands in shared memory (128-token tiles), 2 the kernel with the expanded weights in tensor memory
- * (256-token tiles). */
+ * (256-token tiles).  option 4: chains of captured decode launches (see cb_chain_stats), value 0/1, default 1.
+ * option 5: operand form of the fp16 ring kernel -- 0 (default) packed fields used as fp16 subnormals, 1 fields
+ * OR-ed into 1024.0 with the offset removed per group (for A/B checks of the arithmetic).
+ * These switches are plain process-wide words without locking: set them before issuing work, not concurrently
+ * with calls on other threads. */
 void cb_set_option(int option, int value);
+
+/* Counters of the decode ring kernel's launches issued inside stream capture since the library was loaded
+ * (no counterpart in the reference): counts4[0] launches that began a chain, [1] launches that followed another
+ * launch of this kernel directly on the same capturing stream, [2] of those, launches that were ordered after their
+ * predecessors, [3] of those, launches that ran free.
+ *
+ * What a chain is: while a stream is being captured (cudaStreamBeginCapture / torch.cuda.graph), consecutive calls
+ * of cb_packed_gemv / cb_fused_gate_up / cb_fused_qkv (and their scatter forms) on that stream whose only capture
+ * dependency is the previous such call are linked by programmatic launch edges.  A launch whose x / out / scratch
+ * byte ranges overlap those of no earlier launch that may still be running (weights, bias and rotary tables are
+ * taken to be constant for the duration of the graph) runs FREE: it does not wait for its predecessors and overlaps
+ * them on the GPU, but its grid still completes only after theirs.  Every other launch of the chain is ORDERED: it
+ * waits for the completion of everything before it, exactly as outside a chain.  Any other work captured in between
+ * ends the chain; the next decode call starts a new one with an ordinary full dependency.  Outside capture nothing
+ * of this applies, and cb_set_option(4, 0) switches it off.  No device memory is involved. */
+int cb_chain_stats(long long* counts4);
 
 /* Synchronises the device, then returns in *status the decode kernels' error word and clears it:
  * 0 = no problem; 0 < k < 1000 = in a decode kernel a shared-memory copy of pass k-1 did not arrive

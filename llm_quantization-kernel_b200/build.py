@@ -25,7 +25,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-O3",
-              "--expt-relaxed-constexpr", "-I", INCLUDE] + os.environ.get("CB_EXTRA_NVCC_FLAGS", "").split()
+              "--expt-relaxed-constexpr", "-I", INCLUDE]
 
 
 def nvcc() -> str:

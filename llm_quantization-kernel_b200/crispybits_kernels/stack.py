@@ -23,10 +23,10 @@ Only the linears and the gathers are in the step: attention, normalisation and r
 real model are other kernels and are outside this path.  Each block reads the step's hidden state
 x; inside a block the data flows  x -> QKV -> (Q part) -> o_proj -> gate/up -> down.
 
-The synthetic weights are drawn on the GPU (seeded per block and matrix, identical on every rank) and
-quantised and packed there with plain torch operations that follow the reference's quantizer and
-bitstream bit for bit (Crispybits/Kernel/crispybits_kernels/reference.py:10-55); the tests check this
-against the CPU oracle.
+The synthetic weights are drawn on the stack's device (seeded per block and matrix, identical on every
+rank) and quantised and packed by `packer`: by default the library's GPU kernel (cb_quantize_pack, which is
+bit-identical to the reference's CPU packer); the CPU tests of the sharding arithmetic pass one built on
+their oracle.
 """
 from __future__ import annotations
 
@@ -48,38 +48,13 @@ def sample_bitmap(n_blocks: int = 32, seed: int = 0) -> List[int]:
     return [int(b) for b in rng.choice(np.array([2, 3, 4], dtype=np.int8), size=n_blocks, replace=True)]
 
 
-# ------------------------------------------------------------------ quantise + pack with torch ops (any device)
-@torch.no_grad()
-def quantize_pack(w: torch.Tensor, bits: int, group_size: int = 128, dtype=torch.float16) -> PackedLinearWeight:
-    """Group-wise asymmetric affine quantisation and packing of a float32 [N, K] matrix on its device."""
-    assert bits in (2, 3, 4) and w.dim() == 2
-    n, k = w.shape
-    g = -(-k // group_size)
-    kp = g * group_size
-    wf = torch.zeros(n, kp, dtype=torch.float32, device=w.device)
-    wf[:, :k] = w.float()
-    if kp != k:
-        wf[:, k:] = wf[:, k - 1:k]
-    grp = wf.view(n, g, group_size)
-    qmax = float((1 << bits) - 1)
-    mn, mx = grp.amin(-1), grp.amax(-1)
-    scale = ((mx - mn) / qmax).clamp_min(1e-8)
-    zero = torch.round(-mn / scale).clamp(0, qmax)
-    q = torch.clamp(torch.round(grp / scale[..., None]) + zero[..., None], 0, qmax).view(n, kp)[:, :k].to(torch.int64)
-    c = -(-k // 32)
-    qq = torch.zeros(n, c * 32, dtype=torch.int64, device=w.device)
-    qq[:, :k] = q
-    qq = qq.view(n, c, 32)
-    words = torch.zeros(n, c, bits, dtype=torch.int64, device=w.device)
-    for j in range(32):                         # code j of a chunk sits at bit j*bits of the chunk's stream
-        wi, off = divmod(j * bits, 32)
-        v = qq[:, :, j] << off
-        words[:, :, wi] |= v & 0xFFFFFFFF
-        if off + bits > 32:
-            words[:, :, wi + 1] |= v >> 32
-    words = words.view(n, c * bits)
-    packed = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32).contiguous()
-    return PackedLinearWeight(packed, scale.to(dtype).contiguous(), zero.to(dtype).contiguous(), bits, group_size, k, n)
+# ------------------------------------------------------------------ quantise + pack
+def gpu_packer(w: torch.Tensor, bits: int, group_size: int = 128, dtype=torch.float16) -> PackedLinearWeight:
+    """Quantise and pack a float32 [N, K] CUDA matrix with the library's kernel (cb_quantize_pack, bit-identical to
+    the reference's CPU packer)."""
+    from . import _C
+    packed, scales, zeros = _C.quantize_pack(w, bits, group_size, dtype)
+    return PackedLinearWeight(packed, scales, zeros, bits, group_size, w.shape[1], w.shape[0])
 
 
 def _rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
@@ -106,7 +81,8 @@ class DecodeStack:
 
     def __init__(self, n_blocks: int = 32, d_model: int = 4096, d_ff: int = 11008, bitmap: Optional[List[int]] = None,
                  rank: int = 0, world: int = 1, device="cuda", seed: int = 0, std: float = 0.02, group_size: int = 128,
-                 comm: str = "nccl"):
+                 comm: str = "nccl", packer=None):
+        quantize_pack = packer if packer is not None else gpu_packer
         if d_model % world or d_ff % world or (d_model // world) % 2:
             raise ValueError("d_model and d_ff must divide evenly over the ranks")
         self.n_blocks, self.d_model, self.d_ff = n_blocks, d_model, d_ff

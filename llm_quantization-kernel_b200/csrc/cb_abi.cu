@@ -36,10 +36,10 @@ int sm_count_current() {
     return sms;
 }
 
-int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, int64_t rho, bool pdl,
-                       void* scratch, size_t scratch_bytes, cudaStream_t stream);
-int launch_gemv_direct(int bits, int dtype, const void* x, const GemvParams& P, bool pdl, cudaStream_t stream);
+int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, int64_t rho, bool pdl, bool chains,
+                       int operands, void* scratch, size_t scratch_bytes, cudaStream_t stream);
 int stream_status_read_and_clear(int* out);
+void chain_stats(long long* out4);
 int launch_peer_wait(const GemvParams& P, cudaStream_t stream);
 int launch_peer_signal(const GemvParams& P, cudaStream_t stream);
 int gemm_status_read_and_clear(int* out);
@@ -64,9 +64,9 @@ bool pdl_enabled() {
     return g_pdl != 0;
 }
 static int g_force_generic = 0;
-static int g_no_direct = 0;
 static int g_gemm_kernel = 0;      // 0: by M, 1: shared-memory-operand kernel, 2: weights-in-TMEM kernel
-static int g_prefer_direct = -1;   // -1: by shape, 1: wherever it applies
+static int g_chains = 1;           // captured back-to-back ring launches form chains (cb_chain_stats); cb_set_option(4, 0) switches them off
+static int g_operands = 0;         // fp16 ring kernel operands: 0 subnormal form, 1 with the 1024 offset
 
 int launch_unpack(const int32_t* packed, int64_t n, int64_t K, int bits, int32_t* codes, cudaStream_t stream);
 int launch_quantize_pack(const void* w, int w_dtype, int64_t n, int64_t K, int bits, int64_t gs, int32_t* packed,
@@ -156,19 +156,10 @@ int run_decode(const char* who, const void* x, GemvParams& P, int bits, int64_t 
         P.counters = reinterpret_cast<int*>(scratch);
         P.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kCounterBytes);
     }
-    // The register-streaming kernel is opt-in (cb_set_option(2, 2)).  Measured on B200 it is the faster kernel
-    // for an isolated large matrix at batch 1-2 (22016x4096 W4: 16.1 us against 19.6 us), but inside the
-    // dependent chain of a decode stack, where a launch cannot read its activations before the previous launch
-    // has finished, the ring kernel's step is shorter (1.48 ms against 2.03 ms for the 32-block stack).
-    const bool direct_first = g_prefer_direct == 1;
-    if (!g_force_generic && !g_no_direct && direct_first) {
-        // the register-streaming fp16 kernel when the problem is inside its domain (-1 = it is not)
-        const int rc = launch_gemv_direct(bits, dtype, x, P, pdl_enabled(), stream);
-        if (rc != -1) return rc;
-    }
     if (!g_force_generic) {
-        // then the shared-memory ring kernel
-        const int rc = launch_gemv_stream(bits, dtype, x, P, rho, pdl_enabled(), scratch, scratch_bytes, stream);
+        // the shared-memory ring kernel when the problem is inside its domain (-1 = it is not)
+        const int rc = launch_gemv_stream(bits, dtype, x, P, rho, pdl_enabled(), g_chains != 0, g_operands, scratch,
+                                          scratch_bytes, stream);
         if (rc != -1) return rc;
     }
     // The generic kernels do not carry the rank hand-shake: bracket them with its two halves.
@@ -206,8 +197,9 @@ int cb_sm_count(void) { return sm_count_current(); }
 void cb_set_option(int option, int value) {
     if (option == 0) g_pdl = value ? 1 : 0;
     if (option == 1) g_force_generic = value ? 1 : 0;
-    if (option == 2) { g_no_direct = value == 1 ? 1 : 0; g_prefer_direct = value == 2 ? 1 : -1; }
     if (option == 3) g_gemm_kernel = (value == 1 || value == 2) ? value : 0;
+    if (option == 4) g_chains = value ? 1 : 0;
+    if (option == 5) g_operands = value == 1 ? 1 : 0;
 }
 
 int cb_decode_status(int* status) {
@@ -224,6 +216,12 @@ int cb_decode_status(int* status) {
     return CB_OK;
 }
 int cb_tile_n(void) { return kTileN; }
+
+int cb_chain_stats(long long* counts4) {
+    if (counts4 == nullptr) { set_error("cb_chain_stats: NULL"); return CB_ERR_INVALID; }
+    chain_stats(counts4);
+    return CB_OK;
+}
 
 int cb_max_rho(int bits, int mode) {
     if (!(bits == 2 || bits == 3 || bits == 4)) { set_error("cb_max_rho: bits must be 2/3/4"); return -1; }

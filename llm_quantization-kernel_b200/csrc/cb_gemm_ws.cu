@@ -337,14 +337,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     // release_bar != 0: arrive on that barrier as soon as this warp's last chunk is in registers -- the accumulator may
     // then be overwritten; the conversion and the stores of that chunk follow the arrival.
     auto drain = [&](int tile, int cbegin, int cstep, uint32_t release_bar) {
-#if defined(CB_WS_DIAG) && (CB_WS_DIAG & 4)
-        if (release_bar != 0u) {                      // diagnostic: no accumulator drain (outputs are not written)
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(release_bar);
-        }
-        return;
-#endif
         const int q = warp & 3;
         const int m0 = (tile % P.tiles_m) * kBT;
         const int row = q * 32 + lane;                              // TMEM lane
@@ -431,14 +423,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + bias);
                 }
             }
-#if defined(CB_WS_DIAG) && (CB_WS_DIAG & 8)
-            {   // diagnostic: tensor-memory loads and arithmetic, but (almost) no stores
-                uint32_t h = 0;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) h ^= v[j];
-                if (h == 0x12345678u) nlive = true; else nlive = false;
-            }
-#endif
             int pair_hi = 0;
             if constexpr (!GU) {
                 if constexpr (!QKV) {
@@ -496,19 +480,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         }
     };
 
-#ifdef CB_WS_BARE
-    const bool bare = true;      // diagnostic build: only the MMA issuer and the epilogue run
-#else
-    const bool bare = false;
-#endif
-#if defined(CB_WS_BARE) && CB_WS_BARE == 2
-    const bool with_x = true;
-#else
-    const bool with_x = false;
-#endif
-    if (bare && warp != 1 && !(with_x && warp == 0) && (warp < kFirstEpiWarp || warp == kPackedWarp)) {
-        // nothing
-    } else if (warp == 0) {
+    if (warp == 0) {
         // ================= TMA producer: activation tiles, 256 tokens x 64 codes =================
         if (lane == 0) {
             int it = 0;
@@ -524,11 +496,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         }
     } else if (warp == kPackedWarp) {
         // ================= TMA producer: packed words, 128 rows x 128 codes per box =================
-#if defined(CB_WS_DIAG) && (CB_WS_DIAG & 2)
-        if (false) {                                  // diagnostic: no packed-word traffic
-#else
         if (lane == 0) {
-#endif
             int pit = 0;
             for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x) {
                 int n0 = (tile / P.tiles_m) * kOutCols;
@@ -560,13 +528,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 for (int kb = 0; kb < P.kblocks; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
-#ifndef CB_WS_BARE
                     if (!mbar_wait(full_x(s), ph, abort_flag) || !mbar_wait(full_w(s), ph, abort_flag)) { gave_up = 2; break; }
-#elif CB_WS_BARE == 2
-                    if (!mbar_wait(full_x(s), ph, abort_flag)) { gave_up = 2; break; }     // diagnostic: activations only
-#else
-                    (void)ph;
-#endif
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t xa = base + s * kXBytes;
                     const uint32_t a_tmem = tmem_base + kAccCols + (uint32_t)s * kAStageCols;
@@ -635,9 +597,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         uint32_t meta_next = meta_of(grp);
         for (int pit = 0; pit < total_super && !gave_up; ++pit) {
             const int slot = pit % kPackedSlots;
-#if !(defined(CB_WS_DIAG) && (CB_WS_DIAG & 2))
             if (!__all_sync(0xffffffffu, mbar_wait(full_p(slot), (pit / kPackedSlots) & 1, abort_flag))) { gave_up = 3; break; }
-#endif
             const int half = ((2 * pit) & 3) == grp ? 0 : (((2 * pit + 1) & 3) == grp ? 1 : -1);
             uint32_t w[kWords];
             if (half >= 0) {
@@ -682,13 +642,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     w2[1] = (kq & 1) ? (hi >> 16) : hi;
                 }
                 uint32_t t8[8];
-#if defined(CB_WS_DIAG) && (CB_WS_DIAG & 1)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) t8[j] = w2[j & 1] ^ zz ^ ss;      // diagnostic: no unpack arithmetic
-#else
                 if constexpr (BF) Dequant16B<BITS>::run(w2, zz, ss, t8);
                 else Dequant16<BITS>::run(w2, zz, ss, t8);
-#endif
 #pragma unroll
                 for (int j = 0; j < 8; ++j) t[8 * kq + j] = t8[j];
             }

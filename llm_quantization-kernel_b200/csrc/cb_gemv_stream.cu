@@ -1,29 +1,47 @@
-// Streamlined fp16 decode GEMV for sm_100a: the memory-bound fast path (group size 128, K a multiple
-// of 128, batch <= 8, all three modes).
+// Ring decode GEMV for sm_100a: the memory-bound fast path (fp16 / bf16, group size 128, K a multiple of 256,
+// batch <= 8, all three modes).
 //
-// Why it looks the way it does.  A 4096x4096 W4 matrix is 8.9 MB: at B200's HBM rate that is ~1.4 us
-// of traffic, the same order as one DRAM round trip, so (1) every byte a CTA needs must be in flight
-// at once, and (2) the per-code ALU work must stay far below one instruction per code.
+// Why it looks the way it does.  A 4096x4096 W4 matrix is 8.9 MB: at B200's HBM rate that is ~1.4 us of traffic,
+// the same order as one DRAM round trip and as the hand-over between two kernels of a stream, so (1) every byte a
+// CTA needs must be in flight at once, (2) the per-code ALU work must stay near one instruction per code PAIR, and
+// (3) the stretch between "the activations exist" and "the outputs are stored" must be as short as possible.
 //
-//  (1) Each CTA owns a contiguous slab of virtual output rows (V / #slabs of them, not a multiple of a
-//      tile) and one of split_k K-partitions.  Rows of a slab are fetched 32 at a time ("a pass") with
-//      one cp.async.bulk per row into a shared-memory ring guarded by mbarriers; the copies of the
-//      first passes are issued before anything else, also before the programmatic-dependent-launch
-//      wait, so they overlap the tail of the previous kernel in the stream.  Packed weights are
-//      assumed constant for the duration of the call.
-//  (2) The 8 warps of the CTA split the K-partition by quantisation group.  A warp turns packed words
-//      into exact fp16 integers with the (w & mask) | 0x6400 trick (two codes per LOP3, one HFMA2 to
-//      remove the 1024 offset and the field's power-of-two scale; 3-bit codes are first aligned with
-//      funnel shifts and byte permutes) and feeds them straight to mma.sync m16n8k16 as the A operand:
-//      16 weight rows x 16 codes per instruction, activations of up to 8 batch rows as the B operand,
-//      fp32 accumulation.  Products q*x are exact and sums are fp32, like the reference's
-//      fmaf loop; per group the result enters the row accumulator as  s*D - (s*z)*sum(x)
-//      (Crispybits/Kernel/csrc/packed_gemv.cu:131-135).  Partial sums of the warps meet in shared
-//      memory; split_k > 1 additionally uses the same last-arriver fix-up as the generic kernel.
+//  (1) Each CTA owns a contiguous slab of virtual output rows and one of split_k K-partitions.  Rows of a slab are
+//      fetched 32 (or 16) at a time ("a pass") with one cp.async.bulk per row into a shared-memory ring guarded by
+//      mbarriers; scales and zeros follow as 4-byte cp.async issued by all threads.  The copies of the first passes
+//      are issued before anything else, also before the kernel waits for its predecessor in the stream, so they
+//      overlap the previous kernel.  Packed weights are assumed constant for the duration of the call.
+//  (2) The 8 warps split the K-partition by quantisation group.  A packed word becomes MMA A operands with one
+//      AND per code pair and nothing else (cb_frag.cuh, Frag<>): in fp16 the masked field is read as a subnormal
+//      number, code * 2^(p-24) for a field at bit p, and the activations that meet it are multiplied by 2^-p when
+//      they are staged, once per CTA, in the order the unpack produces codes.  mma.sync m16n8k16 (16 weight rows x
+//      16 codes, up to 8 batch rows as the B operand, fp32 accumulation) then gives 2^-24 * sum(q x) per group; the
+//      zero point enters as  -z * sum(x)  through the accumulator's initial value, the scale as one FMA per group:
+//      acc += s * (sum(q x) - z sum(x))   (Crispybits/Kernel/csrc/packed_gemv.cu:131-135).  The group sums of x come
+//      from eight more MMAs per 8 (group, batch row) pairs with an all-ones A operand.  bf16 has too few mantissa
+//      bits and too small an exponent range for the subnormal form: there (field | 0x4300) = 128 + code is used and
+//      the 128 * sum(x') it adds is subtracted with the zero-point term.
+//  (3) Hand-over.  A launch is a programmatic dependent launch: it may start (and prefetch weights) while its
+//      predecessor in the stream runs, and it waits for the predecessor's completion (griddepcontrol.wait) before it
+//      reads x or writes anything.  That completion event arrives ~1.5 us after the predecessor's last store on this
+//      GPU, which is as long as a 4096x4096 matrix takes to stream.  Inside stream capture the host can do better for
+//      launches that do not depend on one another: consecutive launches of this kernel on one capturing stream form a
+//      CHAIN (a launch whose only capture dependency is the previous launch of this kernel, checked with
+//      cudaStreamGetCaptureInfo; anything else in between starts a new chain).  The host knows the operands of every
+//      launch of a chain, so a launch is one of two kinds:
+//        - ORDERED (the first of a chain, and every launch whose x / out / scratch byte ranges overlap those of a launch
+//          that may still be running): it waits for its predecessor's completion first and lets its own successor start
+//          only after that wait, so a successor that starts knows that everything before the ordered launch is done;
+//        - FREE (no overlap with any launch since the last ordered one): it does not wait at all and overlaps its
+//          predecessors; only its first CTA waits for the predecessor's completion before it EXITS, so grids still
+//          complete in launch order and whatever follows the chain sees all of it.
+//      No device-side state is involved.  Outside capture every launch waits at once and triggers at once, as a plain
+//      programmatic dependent launch does.
 //
-// The dot product is permutation-invariant, so the order in which codes meet MMA k-slots is chosen to
-// suit the unpack: activations are staged once per CTA in that same order ("x fragments").
+// The dot product is permutation-invariant, so the order in which codes meet MMA k-slots is chosen to suit the unpack.
 #include <algorithm>
+#include <map>
+#include <mutex>
 
 #include "cb_common.cuh"
 #include "cb_frag.cuh"
@@ -31,49 +49,34 @@
 namespace cb {
 namespace {
 
-constexpr int kThreads = 256;
 constexpr int kWarps = 8;
-constexpr int kMaxRowsPerPass = 32;       // a pass is one or two 16-row MMA tiles (StreamParams::rpp)
+constexpr int kThreads = 32 * kWarps;
+constexpr int kRowLanes = kThreads / 32;        // threads that share one row of a pass when copies are issued and results reduced
 constexpr int kMaxBuf = 6;
-constexpr int kSpinLimit = 1 << 22;       // bounded mbarrier wait (~ a second), then give up and flag
+constexpr int kSpinLimit = 1 << 22;           // bounded mbarrier wait (~ a second), then give up and flag
 constexpr size_t kSmemCap = 220 * 1024;       // one CTA per SM
 constexpr size_t kSmemCapTwo = 112 * 1024;    // two CTAs per SM
 
-__device__ int g_stream_status;
-#ifdef CB_STREAM_TIMING
-// Diagnostic build only: per-CTA nanosecond timestamps of the kernel's phases.
-__device__ unsigned long long g_stream_times[1024][8];
-__device__ __forceinline__ unsigned long long now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define CB_STAMP(i) do { if (threadIdx.x == 0 && blockIdx.x < 1024) { g_stream_times[blockIdx.x][i] = now_ns(); \
-    if ((i) == 0) g_stream_times[blockIdx.x][7] = (unsigned long long)clock64(); \
-    if ((i) == 6) g_stream_times[blockIdx.x][7] = (unsigned long long)clock64() - g_stream_times[blockIdx.x][7]; } } while (0)
-#else
-#define CB_STAMP(i) do { } while (0)
-#endif           // 0 = ok; else the pass whose copy never landed, plus one
+__device__ int g_stream_status;               // 0 = ok; k > 0: the copy of pass k-1 never landed
 
-#ifdef CB_STREAM_DEBUG
-#define CB_DBG(bit) (S.dbg & (bit))
-#else
-#define CB_DBG(bit) 0
-#endif
+// How a launch relates to its predecessor in the stream (see the head of this file).
+constexpr int kLaunchPlain = 0;      // wait at once, trigger at once (outside stream capture)
+constexpr int kLaunchOrdered = 1;    // wait, then trigger (captured chain: this launch depends on earlier ones)
+constexpr int kLaunchFree = 2;       // trigger at once, never wait before working; the first CTA waits before it exits
 
 struct StreamParams {
     GemvParams g;
     int nslabs;            // CTAs per K-partition
     int nbuf;              // ring depth
     int rpp;               // rows per pass: 32 or 16
-    int dbg;               // diagnostic builds only: parts of the kernel to leave out
     int pitch;             // shared-memory bytes per staged row (row bytes + bank-spreading pad)
     int meta_stride;       // shared-memory bytes per staged row of scales (and of zeros)
     int slot_bytes;        // one ring slot: rpp weight rows, rpp scale rows, rpp zero rows
-    int xb_stride;         // shared-memory bytes between batch rows of the staged activations
-    int pair_q, pair_r;    // row pairs per slab: quotient and remainder of (V/2) / nslabs
+    int row_gran;          // slabs begin at multiples of this many virtual rows
+    int pair_q, pair_r;    // row units per slab: quotient and remainder of ceil(V / row_gran) / nslabs
     int grp_q, grp_r;      // group PAIRS per K-partition: quotient and remainder of (groups/2) / split_k
-    unsigned off_x, off_red, off_ring, off_bar;   // shared-memory carve-up
+    unsigned off_red, off_xs, off_xsum, off_ring, off_bar;   // shared-memory carve-up
+    int launch_kind;       // kLaunchPlain / kLaunchOrdered / kLaunchFree
 };
 
 // ---- small PTX wrappers ------------------------------------------------------------------------
@@ -94,10 +97,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -105,31 +104,61 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+// Shared-memory loads through 32-bit shared-window addresses (no generic-pointer arithmetic in the inner loop).
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ unsigned short lds16(uint32_t a) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t a, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 // One chunk (BITS words) from shared memory with the widest load its alignment allows.
-template <int BITS> __device__ __forceinline__ void lds_chunk(const unsigned char* p, uint32_t (&w)[BITS]) {
+template <int BITS> __device__ __forceinline__ void lds_chunk(uint32_t a, uint32_t (&w)[BITS]) {
     if constexpr (BITS == 4) {
-        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const uint4 v = lds128(a);
         w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
     } else if constexpr (BITS == 2) {
-        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        const uint2 v = lds64(a);
         w[0] = v.x; w[1] = v.y;
     } else {
-        const uint32_t* q = reinterpret_cast<const uint32_t*>(p);
-        w[0] = q[0]; w[1] = q[1]; w[2] = q[2];
+        w[0] = lds32(a); w[1] = lds32(a + 4); w[2] = lds32(a + 8);
     }
 }
+template <bool BF> __device__ __forceinline__ float meta_f32(unsigned short bits) {
+    if constexpr (BF) return __uint_as_float((uint32_t)bits << 16);
+    else return __half2float(__ushort_as_half(bits));
+}
 
-template <int BITS, bool BF>
+constexpr int kXBlock = 80;   // bytes between staged activation blocks: 64 of data, 16 of padding (conflict-free 16-byte reads)
+
+template <int BITS, int KIND>
 __global__ void __launch_bounds__(kThreads, 2)
-gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
-    // BF: activations, scales, zeros and outputs are bfloat16 (the pointer types below only stand for "16-bit elements")
-    using U = std::conditional_t<BF, UnpackB<BITS>, Unpack<BITS>>;
+gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
+    // x is read with L2-coherent loads only (ld.global.cg): it is written while this grid is already resident, by the
+    // previous kernel of the stream or, in a column-parallel stack, by peer GPUs.
+    using F = Frag<BITS, KIND>;
+    constexpr bool BF = F::kBf;      // activations, scales, zeros and outputs are bfloat16
     using OutT = std::conditional_t<BF, __nv_bfloat16, __half>;
     extern __shared__ __align__(128) unsigned char smem[];
-    // The next kernel of the stream may start right away: it only prefetches its own weights until
-    // this grid has completed.
-    asm volatile("griddepcontrol.launch_dependents;");
-    CB_STAMP(0);
+    // The next kernel of the stream may start right away: it only prefetches its own weights until this grid lets it
+    // go on.  An ordered launch of a captured chain holds its successor back until its own wait is over (below).
+    if (S.launch_kind != kLaunchOrdered) asm volatile("griddepcontrol.launch_dependents;");
     const GemvParams& P = S.g;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -141,94 +170,176 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
     if (P.split_k > 1) { split = blockIdx.x % P.split_k; slab = blockIdx.x / P.split_k; }
     const int g_begin = 2 * split_begin(split, S.grp_q, S.grp_r);
     const int ng = 2 * split_begin(split + 1, S.grp_q, S.grp_r) - g_begin;
-    const int row_begin = 2 * split_begin(slab, S.pair_q, S.pair_r);
-    const int row_end = min(P.V, 2 * split_begin(slab + 1, S.pair_q, S.pair_r));
+    const int row_begin = S.row_gran * split_begin(slab, S.pair_q, S.pair_r);
+    const int row_end = min(P.V, S.row_gran * split_begin(slab + 1, S.pair_q, S.pair_r));
     const int rpp = S.rpp;
     const int npass = (row_end - row_begin + rpp - 1) / rpp;
     const uint32_t row_bytes = (uint32_t)ng * kGroupBytes;
 
     const uint32_t s_base = smem_u32(smem);
-    const uint32_t s_ring = s_base + S.off_ring, s_bar = s_base + S.off_bar;
-    float* red = reinterpret_cast<float*>(smem + S.off_red);         // [2][warps][2 tiles][32 lanes][4]
+    const uint32_t s_ring = s_base + S.off_ring, s_bar = s_base + S.off_bar, s_xs = s_base + S.off_xs;
+    const uint32_t s_zero = s_base + S.off_bar + 64;      // 64 zero bytes: what lanes without a batch row load as activations
+    // per pass parity: partial sums [warps][2 tiles][8 row pairs][tcols lanes][4], then zero-point terms [warps][32 rows][B]
+    float* red = reinterpret_cast<float*>(smem + S.off_red);
+    const int tcols = (P.B + 1) >> 1;                 // lanes t < tcols hold batch columns below B
+    const int acc_floats = kWarps * 2 * 8 * tcols * 4;
+    const int red_floats = acc_floats + kWarps * 32 * P.B;
 
     if (tid == 0) {
-        for (int b = 0; b < S.nbuf; ++b) mbar_init(s_bar + 8 * b, 33);
+        for (int b = 0; b < S.nbuf; ++b) mbar_init(s_bar + 8 * b, kThreads + 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (tid < 16) reinterpret_cast<uint32_t*>(smem + S.off_bar + 64)[tid] = 0u;
     __syncthreads();
 
-    // Issue the copies of pass `p` into ring slot p % nbuf (warp 0, one row per lane): the packed row
-    // with one bulk copy, its scales and zeros with 4-byte cp.async.  The slot's mbarrier completes
-    // after the expect-tx arrival, the bulk bytes, and one arrival per lane once its cp.async landed.
+    // Issue the copies of pass `p` into ring slot p % nbuf.  Thread = (row of the pass, one eighth of the row's group
+    // pairs).  The first thread of a row issues one bulk copy for the packed row (four rows per warp: bulk copies of
+    // one warp are issued one after the other); every thread copies its share of the row's scales and zeros, 4 bytes
+    // (two groups) per cp.async.  The slot's mbarrier completes after the expect-tx arrival, the bulk bytes, and one
+    // arrival per thread once its cp.async have landed.
     auto issue_pass = [&](int p) {
         const int buf = p % S.nbuf;
         const int row0 = row_begin + p * rpp;
         const int nrows = min(rpp, row_end - row0);
         const uint32_t slot = s_ring + (uint32_t)buf * S.slot_bytes;
         const uint32_t bar = s_bar + 8 * buf;
-        if (lane == 0) mbar_expect_tx(bar, CB_DBG(4) ? 0u : (uint32_t)nrows * row_bytes);
-        __syncwarp();
-        if (lane < nrows) {
+        if (tid == 0) mbar_expect_tx(bar, (uint32_t)nrows * row_bytes);
+        const int r = tid / kRowLanes;
+        if (r < nrows) {
             int proj, lr;
-            map_row(P, row0 + lane, proj, lr);
-            const unsigned char* src = reinterpret_cast<const unsigned char*>(P.p[proj].w) +
-                                       ((size_t)lr * P.wpr * 4 + (size_t)g_begin * kGroupBytes);
-            if (!CB_DBG(4)) bulk_g2s(slot + (uint32_t)lane * S.pitch, src, row_bytes, bar);
+            map_row(P, row0 + r, proj, lr);
+            if ((tid % kRowLanes) == 0) {
+                const unsigned char* src = reinterpret_cast<const unsigned char*>(P.p[proj].w) +
+                                           ((size_t)lr * P.wpr * 4 + (size_t)g_begin * kGroupBytes);
+                bulk_g2s(slot + (uint32_t)r * S.pitch, src, row_bytes, bar);
+            }
             const __half* ssrc = reinterpret_cast<const __half*>(P.p[proj].s) + (size_t)lr * P.groups + g_begin;
             const __half* zsrc = reinterpret_cast<const __half*>(P.p[proj].z) + (size_t)lr * P.groups + g_begin;
-            const uint32_t sdst = slot + rpp * S.pitch + (uint32_t)lane * S.meta_stride;
+            const uint32_t sdst = slot + rpp * S.pitch + (uint32_t)r * S.meta_stride;
             const uint32_t zdst = sdst + rpp * S.meta_stride;
-            for (int j = 0; j < (CB_DBG(1) ? 0 : ng); j += 2) {
+            for (int j = 2 * (tid % kRowLanes); j < ng; j += 2 * kRowLanes) {
                 cp_async4(sdst + 2 * j, ssrc + j);
                 cp_async4(zdst + 2 * j, zsrc + j);
             }
         }
         cp_async_arrive_noinc(bar);
     };
-    if (warp == 0) {
-        for (int p = 0; p < min(npass, S.nbuf); ++p) issue_pass(p);
+    for (int p = 0; p < min(npass, S.nbuf); ++p) issue_pass(p);
+    // Touch the activations' pages now (the values may be stale and are not used): address translation and the
+    // request path are then warm when the real loads follow the hand-over.
+    if (lane == 0) {
+        unsigned int sink;
+        asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(sink) : "l"(x + 2 * (size_t)(warp % P.B) * P.K + 256 * (size_t)(g_begin + (ng * warp) / kWarps)));
     }
-    CB_STAMP(1);
 
     // ---- this warp's groups inside the K-partition
-    const int wg_begin = (ng * warp) >> 3, wg_end = (ng * (warp + 1)) >> 3;
-
-    // Wait until everything the previous kernel wrote (our activations, the scratch) is visible.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const unsigned int peer_epoch = peer_wait(P);      // sharded stacks: the peers' slices of our activations have landed
-    CB_STAMP(2);
-
-    const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
-    // Lane (g, t) supplies the MMA B fragments of batch row g: the 32 activations of chunk t of each
-    // group, read straight from global memory one group ahead of their use (the vector is small and
-    // stays in L1/L2; staging it in shared memory would cost a CTA-wide barrier).
-    const bool has_x = g < P.B;
-    const __half* xrow = x + (size_t)(has_x ? g : 0) * P.K + (size_t)g_begin * 128 + t * 32;
-    auto load_x = [&](int gl, uint32_t (&r)[16]) {
-        if (has_x && gl < wg_end) {
-            const uint4* xp = reinterpret_cast<const uint4*>(xrow + (size_t)gl * 128);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint4 v = __ldg(xp + i);
-                r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = 0u;
-        }
-    };
-    uint32_t xnext[16];
-    load_x(wg_begin, xnext);
+    const int wg_begin = (ng * warp) / kWarps, wg_end = (ng * (warp + 1)) / kWarps;
     int failed = 0;
-    CB_STAMP(3);
 
+    // ---- hand-over: after this block everything this launch depends on (its activations, earlier readers and writers of
+    //      its outputs, the scratch) is complete and visible.  A free launch depends on nothing that may still run.
+    if (S.launch_kind != kLaunchFree) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (S.launch_kind == kLaunchOrdered) asm volatile("griddepcontrol.launch_dependents;");
+    }
+    const unsigned int peer_epoch = peer_wait(P);      // sharded stacks: the peers' slices of our activations have landed
+
+    // ---- activations of this warp's groups -> shared memory in MMA B-fragment order, scaled by 2^-shift; group sums.
+    // One task = the 32 activations that one (batch row b, group, chunk t) contributes: a lane loads them, re-pairs
+    // them to the unpack order and stores the 16 registers that lane (g = b, t) of the main loop will load back.
+    // The four lanes of a quad hold the four chunks of one (group, batch row), i.e. one column of an MMA B operand:
+    // eight MMAs with an all-ones A operand add the 128 values up in fp32 for the eight quads at once.
+    float* xsum = reinterpret_cast<float*>(smem + S.off_xsum);         // [group][8]: sum(x) / unit, then [group][8]: base * sum(x')
+    {
+        const int ntask = (wg_end - wg_begin) * P.B * 4;
+        for (int first = 0; first < ntask; first += 32) {
+            const int id = first + lane;
+            const bool on = id < ntask;
+            const int q = id >> 2, tq = id & 3;
+            const int gl = wg_begin + q / P.B, b = q % P.B;
+            uint32_t raw[16];
+            if (on) {
+                const uint4* xp = reinterpret_cast<const uint4*>(x + 2 * ((size_t)b * P.K + (size_t)(g_begin + gl) * 128 + tq * 32));
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint4 v = __ldcg(xp + i);
+                    raw[4 * i] = v.x; raw[4 * i + 1] = v.y; raw[4 * i + 2] = v.z; raw[4 * i + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) raw[i] = 0u;
+            }
+            // group sums first: the MMAs run while the activations are re-paired and stored
+            const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+            float sa[4], sb[4], sc[4], sd[4];
+            auto mma = [](float (&d)[4], uint32_t a, uint32_t b0, uint32_t b1, const float (&c)[4]) {
+                if constexpr (BF) mma16816_bf16(d, a, a, a, a, b0, b1, c);
+                else mma16816(d, a, a, a, a, b0, b1, c);
+            };
+            mma(sa, F::kOnes, raw[0], raw[1], zero4);
+            mma(sb, F::kOnes, raw[2], raw[3], zero4);
+            mma(sc, F::kOnes, raw[4], raw[5], zero4);
+            mma(sd, F::kOnes, raw[6], raw[7], zero4);
+            mma(sa, F::kOnes, raw[8], raw[9], sa);
+            mma(sb, F::kOnes, raw[10], raw[11], sb);
+            mma(sc, F::kOnes, raw[12], raw[13], sc);
+            mma(sd, F::kOnes, raw[14], raw[15], sd);
+            uint32_t xf[16];
+#pragma unroll
+            for (int m = 0; m < 16; ++m) {
+                const int lo = F::pair_lo(m), hi = lo + F::pair_gap();
+                xf[m] = __byte_perm(raw[lo >> 1], raw[hi >> 1], (lo & 1) ? 0x7632 : 0x5410);
+                if (F::shift(m) != 0) xf[m] = F::mul2(xf[m], F::pow2neg(F::shift(m)));
+            }
+            if (on) {
+                const uint32_t dst = s_xs + (uint32_t)(((gl * P.B + b) * 4 + tq) * kXBlock);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sts128(dst + 16 * i, make_uint4(xf[4 * i], xf[4 * i + 1], xf[4 * i + 2], xf[4 * i + 3]));
+            }
+            float x0 = (sa[0] + sb[0]) + (sc[0] + sd[0]), x1 = (sa[1] + sb[1]) + (sc[1] + sd[1]);
+            float c0 = 0.f, c1 = 0.f;
+            if constexpr (F::kBase != 0.f) {
+                mma(sa, F::kOnes, xf[0], xf[1], zero4);
+                mma(sb, F::kOnes, xf[2], xf[3], zero4);
+                mma(sc, F::kOnes, xf[4], xf[5], zero4);
+                mma(sd, F::kOnes, xf[6], xf[7], zero4);
+                mma(sa, F::kOnes, xf[8], xf[9], sa);
+                mma(sb, F::kOnes, xf[10], xf[11], sb);
+                mma(sc, F::kOnes, xf[12], xf[13], sc);
+                mma(sd, F::kOnes, xf[14], xf[15], sd);
+                c0 = F::kBase * ((sa[0] + sb[0]) + (sc[0] + sd[0]));
+                c1 = F::kBase * ((sa[1] + sb[1]) + (sc[1] + sd[1]));
+            }
+            // lane l < 4 holds columns 2l and 2l+1, i.e. the quads 2l and 2l+1 of this round
+            if (lane < 4) {
+                const int q0 = (first >> 2) + 2 * lane;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int qq = q0 + j;
+                    if (4 * qq < ntask) {
+                        const int at = (wg_begin + qq / P.B) * 8 + qq % P.B;
+                        xsum[at] = (j ? x1 : x0) * (1.0f / F::kInvUnit);
+                        if constexpr (F::kBase != 0.f) xsum[S.g.groups * 8 + at] = j ? c1 : c0;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    // Lane (g, t) of the main loop supplies the MMA B fragments of batch row g: lanes without a batch row read zeros.
+    const bool has_x = g < P.B;
+    const uint32_t x_lane0 = has_x ? s_xs + (uint32_t)(((wg_begin * P.B + g) * 4 + t) * kXBlock) : s_zero;
+    const uint32_t x_step = has_x ? (uint32_t)(P.B * 4 * kXBlock) : 0u;
+    const uint32_t p8 = 8u * S.pitch, m8 = 8u * S.meta_stride;
+    const int ngw = wg_end - wg_begin;
     for (int p = 0; p < npass; ++p) {
         const int buf = p % S.nbuf;
         const int row0 = row_begin + p * rpp;
         const uint32_t parity = (uint32_t)((p / S.nbuf) & 1);
         const int ntile = (min(rpp, row_end - row0) + 15) >> 4;
-        const unsigned char* rbase = smem + S.off_ring + (size_t)buf * S.slot_bytes;
-        float* myred = red + (size_t)(p & 1) * (kWarps * 2 * 32 * 4);
+        const uint32_t slot = s_ring + (uint32_t)buf * S.slot_bytes;
+        float* myred = red + (size_t)(p & 1) * red_floats;
         {   // bounded wait for this pass's rows
             int spins = 0;
             const uint32_t bar = s_bar + 8 * buf;
@@ -236,113 +347,191 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
                 if (++spins > kSpinLimit) { failed = p + 1; break; }
             }
         }
-        if (p == 0) CB_STAMP(4);
         float acc[2][4];
 #pragma unroll
         for (int i = 0; i < 2; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        // Rows past the end of the slab were never copied: their ring bytes are stale.  They only feed accumulator
+        // rows that are never stored (rows are independent in the MMA), so nothing masks them here.
+        uint32_t w_at = slot + (uint32_t)g * S.pitch + (uint32_t)(t * kChunkBytes + wg_begin * kGroupBytes);   // row g, this lane's chunk
+        uint32_t m_at = slot + (uint32_t)rpp * S.pitch + (uint32_t)g * S.meta_stride + 2u * wg_begin;          // scale of row g
+        uint32_t x_at = x_lane0;
 
-        for (int gl = wg_begin; gl < (CB_DBG(2) ? wg_begin : wg_end); ++gl) {
-            // activations of this group, re-paired to match the unpack order; the next group's are requested now
+        // One step = one group of this warp against TILES 16-row tiles of the pass: sum(q x) per (row, batch column),
+        // times the scale.  Both tiles sit in one straight-line block so that the unpack of one overlaps the MMAs of
+        // the other (a dependent mma.sync issues 110-150 cycles after its predecessor on this GPU; four independent
+        // accumulation chains of depth two per tile).
+        auto step = [&](auto tiles_tag, int tile0) {
+            constexpr int TILES = decltype(tiles_tag)::value;
+            const bool advance = TILES == 2 || tile0 == ntile - 1;
             uint32_t xf[16];
 #pragma unroll
-            for (int m = 0; m < 16; ++m) {
-                const int lo = U::pair_lo(m), hi = lo + U::pair_gap();
-                xf[m] = __byte_perm(xnext[lo >> 1], xnext[hi >> 1], (lo & 1) ? 0x7632 : 0x5410);
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = lds128(x_at + 16 * i);
+                xf[4 * i] = v.x; xf[4 * i + 1] = v.y; xf[4 * i + 2] = v.z; xf[4 * i + 3] = v.w;
             }
-            if (!CB_DBG(8)) load_x(gl + 1 < wg_end ? gl + 1 : wg_begin, xnext);      // wraps to the first group for the next pass
+            uint32_t wa[TILES][BITS], wb[TILES][BITS];
+            float s0[TILES], s1[TILES];
 #pragma unroll
-            for (int tile = 0; tile < 2; ++tile) {
-                if (tile < ntile) {
-                    const unsigned char* arow = rbase + (size_t)(tile * 16 + g) * S.pitch + (size_t)gl * kGroupBytes + (size_t)t * kChunkBytes;
-                    const __half* s0 = reinterpret_cast<const __half*>(rbase + rpp * S.pitch + (size_t)(tile * 16 + g) * S.meta_stride);
-                    const __half* s1 = s0 + 4 * S.meta_stride;                       // 8 rows further (stride is in bytes, pointer in halves)
-                    const __half* z0 = s0 + (rpp / 2) * S.meta_stride;               // the zeros follow the scale rows
-                    const __half* z1 = z0 + 4 * S.meta_stride;
-                    // rows past the end of the slab were never copied: give them scale 0 and a finite zero point
-                    const bool ok0 = row0 + tile * 16 + g < row_end, ok1 = row0 + tile * 16 + g + 8 < row_end;
-                    const float cs0 = ok0 ? to_f32(reinterpret_cast<const OutT*>(s0)[gl]) : 0.f, cs1 = ok1 ? to_f32(reinterpret_cast<const OutT*>(s1)[gl]) : 0.f;
-                    const uint32_t zr0 = ok0 ? (uint32_t)reinterpret_cast<const unsigned short*>(z0)[gl] : 0u;
-                    const uint32_t zr1 = ok1 ? (uint32_t)reinterpret_cast<const unsigned short*>(z1)[gl] : 0u;
-                    uint32_t ka[U::kConsts], kb[U::kConsts];
-                    U::consts(zr0 | (zr0 << 16), ka);
-                    U::consts(zr1 | (zr1 << 16), kb);
-                    uint32_t wa[BITS], wb[BITS], ea[16], eb[16];
-                    lds_chunk<BITS>(arow, wa);
-                    lds_chunk<BITS>(arow + 8 * (size_t)S.pitch, wb);
-                    if (CB_DBG(32)) {
+            for (int tile = 0; tile < TILES; ++tile) {
+                lds_chunk<BITS>(w_at + 2 * (tile + tile0) * p8, wa[tile]);
+                lds_chunk<BITS>(w_at + (2 * (tile + tile0) + 1) * p8, wb[tile]);
+                s0[tile] = meta_f32<BF>(lds16(m_at + 2 * (tile + tile0) * m8));
+                s1[tile] = meta_f32<BF>(lds16(m_at + (2 * (tile + tile0) + 1) * m8));
+            }
+            float d[TILES][4][4];
+            const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+            auto mma = [](float (&dd)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
+                          const float (&c)[4]) {
+                if constexpr (BF) mma16816_bf16(dd, a0, a1, a2, a3, b0, b1, c);
+                else mma16816(dd, a0, a1, a2, a3, b0, b1, c);
+            };
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) { ea[i] = wa[i % BITS] + ka[0]; eb[i] = wb[i % BITS] + kb[0]; }
-                    } else {
-                    U::run(wa, ka, ea);
-                    U::run(wb, kb, eb);
-                    }
-                    // Four independent accumulation chains of depth two: on this GPU a dependent mma.sync
-                    // issues ~110 cycles after its predecessor, so the eight k-steps must not form one chain.
-                    float d0[4], d1[4], d2[4], d3[4];
-                    if (CB_DBG(16)) {
-                        uint32_t h = 0;
+            for (int tile = 0; tile < TILES; ++tile) {
+                uint32_t ea[16], eb[16];
+                F::run(wa[tile], ea);
+                F::run(wb[tile], eb);
+                mma(d[tile][0], ea[0], eb[0], ea[1], eb[1], xf[0], xf[1], zero4);
+                mma(d[tile][1], ea[2], eb[2], ea[3], eb[3], xf[2], xf[3], zero4);
+                mma(d[tile][2], ea[4], eb[4], ea[5], eb[5], xf[4], xf[5], zero4);
+                mma(d[tile][3], ea[6], eb[6], ea[7], eb[7], xf[6], xf[7], zero4);
+                mma(d[tile][0], ea[8], eb[8], ea[9], eb[9], xf[8], xf[9], d[tile][0]);
+                mma(d[tile][1], ea[10], eb[10], ea[11], eb[11], xf[10], xf[11], d[tile][1]);
+                mma(d[tile][2], ea[12], eb[12], ea[13], eb[13], xf[12], xf[13], d[tile][2]);
+                mma(d[tile][3], ea[14], eb[14], ea[15], eb[15], xf[14], xf[15], d[tile][3]);
+            }
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) h ^= ea[i] ^ eb[i] ^ xf[i];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) { d0[j] = __uint_as_float(h & 0x3fffffff); d1[j] = d2[j] = d3[j] = 0.f; }
-                    } else {
-                    auto mma = [](float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
-                                  const float (&c)[4]) {
-                        if constexpr (BF) mma16816_bf16(d, a0, a1, a2, a3, b0, b1, c);
-                        else mma16816(d, a0, a1, a2, a3, b0, b1, c);
-                    };
-                    mma(d0, ea[0], eb[0], ea[1], eb[1], xf[0], xf[1], zero4);
-                    mma(d1, ea[2], eb[2], ea[3], eb[3], xf[2], xf[3], zero4);
-                    mma(d2, ea[4], eb[4], ea[5], eb[5], xf[4], xf[5], zero4);
-                    mma(d3, ea[6], eb[6], ea[7], eb[7], xf[6], xf[7], zero4);
-                    mma(d0, ea[8], eb[8], ea[9], eb[9], xf[8], xf[9], d0);
-                    mma(d1, ea[10], eb[10], ea[11], eb[11], xf[10], xf[11], d1);
-                    mma(d2, ea[12], eb[12], ea[13], eb[13], xf[12], xf[13], d2);
-                    mma(d3, ea[14], eb[14], ea[15], eb[15], xf[14], xf[15], d3);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) { d0[j] = (d0[j] + d1[j]) + (d2[j] + d3[j]); d1[j] = 0.f; }
-                    // acc += s * sum((q - z) x): rows g (d[0], d[1]) and g+8 (d[2], d[3]), batch columns 2t, 2t+1
-                    acc[tile][0] = fmaf(cs0, d0[0] + d1[0], acc[tile][0]);
-                    acc[tile][1] = fmaf(cs0, d0[1] + d1[1], acc[tile][1]);
-                    acc[tile][2] = fmaf(cs1, d0[2] + d1[2], acc[tile][2]);
-                    acc[tile][3] = fmaf(cs1, d0[3] + d1[3], acc[tile][3]);
+            for (int tile = 0; tile < TILES; ++tile) {
+                const float q0 = (d[tile][0][0] + d[tile][1][0]) + (d[tile][2][0] + d[tile][3][0]);
+                const float q1 = (d[tile][0][1] + d[tile][1][1]) + (d[tile][2][1] + d[tile][3][1]);
+                const float q2 = (d[tile][0][2] + d[tile][1][2]) + (d[tile][2][2] + d[tile][3][2]);
+                const float q3 = (d[tile][0][3] + d[tile][1][3]) + (d[tile][2][3] + d[tile][3][3]);
+                if (TILES == 2 ? tile == 0 : tile0 == 0) {
+                    acc[0][0] = fmaf(s0[tile], q0, acc[0][0]); acc[0][1] = fmaf(s0[tile], q1, acc[0][1]);
+                    acc[0][2] = fmaf(s1[tile], q2, acc[0][2]); acc[0][3] = fmaf(s1[tile], q3, acc[0][3]);
+                } else {
+                    acc[1][0] = fmaf(s0[tile], q0, acc[1][0]); acc[1][1] = fmaf(s0[tile], q1, acc[1][1]);
+                    acc[1][2] = fmaf(s1[tile], q2, acc[1][2]); acc[1][3] = fmaf(s1[tile], q3, acc[1][3]);
                 }
             }
+            if (advance) {
+                w_at += kGroupBytes;
+                m_at += 2;
+                x_at += x_step;
+            }
+        };
+        if (ntile == 2) {
+            for (int i = 0; i < ngw; ++i) step(std::integral_constant<int, 2>{}, 0);
+        } else {
+            for (int i = 0; i < ngw; ++i) {
+                step(std::integral_constant<int, 1>{}, 0);
+                if (ntile == 2) step(std::integral_constant<int, 1>{}, 1);
+            }
         }
-        // ---- hand the partial sums to the reduction (other warps covered other groups)
+        // ---- zero-point (and operand-base) terms of this warp's groups: lane = row of the pass,
+        //      sum over groups of  s * (z * sum(x) + base * sum(x'))  per batch row
+        {
+            // (a pass of 16 rows stages 16 rows of metadata: lanes past it compute a value nobody reads)
+            uint32_t ms = slot + (uint32_t)rpp * S.pitch + (uint32_t)(lane < rpp ? lane : 0) * S.meta_stride + 2u * wg_begin;
+            const uint32_t zoff = (uint32_t)rpp * S.meta_stride;
+            float* cdst = myred + acc_floats + (warp * 32 + lane) * P.B;
+            const float* xs0 = xsum + wg_begin * 8;
+            if (P.B <= 2) {
+                float c0 = 0.f, c1 = 0.f;
+                for (int i = 0; i < ngw; ++i, ms += 2, xs0 += 8) {
+                    const float sc = meta_f32<BF>(lds16(ms));
+                    const float sz = sc * meta_f32<BF>(lds16(ms + zoff));
+                    const float2 xz = *reinterpret_cast<const float2*>(xs0);
+                    c0 = fmaf(sz, xz.x, c0);
+                    c1 = fmaf(sz, xz.y, c1);
+                    if constexpr (F::kBase != 0.f) {
+                        const float2 xc = *reinterpret_cast<const float2*>(xs0 + S.g.groups * 8);
+                        c0 = fmaf(sc, xc.x, c0);
+                        c1 = fmaf(sc, xc.y, c1);
+                    }
+                }
+                cdst[0] = c0;
+                if (P.B == 2) cdst[1] = c1;
+            } else {
+                float c[8];
 #pragma unroll
-        for (int tile = 0; tile < 2; ++tile)
-            *reinterpret_cast<float4*>(&myred[((warp * 2 + tile) * 32 + lane) * 4]) =
-                make_float4(acc[tile][0], acc[tile][1], acc[tile][2], acc[tile][3]);
-        if (p == 0) CB_STAMP(5);
+                for (int j = 0; j < 8; ++j) c[j] = 0.f;
+                for (int i = 0; i < ngw; ++i, ms += 2, xs0 += 8) {
+                    const float sc = meta_f32<BF>(lds16(ms));
+                    const float sz = sc * meta_f32<BF>(lds16(ms + zoff));
+                    const float4 xa = *reinterpret_cast<const float4*>(xs0);
+                    const float4 xb = *reinterpret_cast<const float4*>(xs0 + 4);
+                    c[0] = fmaf(sz, xa.x, c[0]); c[1] = fmaf(sz, xa.y, c[1]); c[2] = fmaf(sz, xa.z, c[2]); c[3] = fmaf(sz, xa.w, c[3]);
+                    c[4] = fmaf(sz, xb.x, c[4]); c[5] = fmaf(sz, xb.y, c[5]); c[6] = fmaf(sz, xb.z, c[6]); c[7] = fmaf(sz, xb.w, c[7]);
+                    if constexpr (F::kBase != 0.f) {
+                        const float4 ca = *reinterpret_cast<const float4*>(xs0 + S.g.groups * 8);
+                        const float4 cb = *reinterpret_cast<const float4*>(xs0 + S.g.groups * 8 + 4);
+                        c[0] = fmaf(sc, ca.x, c[0]); c[1] = fmaf(sc, ca.y, c[1]); c[2] = fmaf(sc, ca.z, c[2]); c[3] = fmaf(sc, ca.w, c[3]);
+                        c[4] = fmaf(sc, cb.x, c[4]); c[5] = fmaf(sc, cb.y, c[5]); c[6] = fmaf(sc, cb.z, c[6]); c[7] = fmaf(sc, cb.w, c[7]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (j < P.B) cdst[j] = c[j];
+            }
+        }
+        // ---- hand the partial sums to the reduction (other warps covered other groups): lanes whose batch columns exist
+        if (t < tcols) {
+#pragma unroll
+            for (int tile = 0; tile < 2; ++tile)
+                *reinterpret_cast<float4*>(&myred[(((warp * 2 + tile) * 8 + g) * tcols + t) * 4]) =
+                    make_float4(acc[tile][0], acc[tile][1], acc[tile][2], acc[tile][3]);
+        }
         __syncthreads();
         // the ring slot is free again: refill it with pass p + nbuf
-        if (warp == 0 && p + S.nbuf < npass) {
+        if (p + S.nbuf < npass) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue_pass(p + S.nbuf);
         }
         {
-            // thread -> (tile, row in tile, batch column)
-            const int tile = tid >> 7, r = (tid >> 3) & 15, b = tid & 7;
-            const int v = row0 + tile * 16 + r;
-            const int fl = (r & 7) * 4 + (b >> 1), fe = (r >> 3) * 2 + (b & 1);
-            const int pl = ((r ^ 1) & 7) * 4 + (b >> 1);
-            float mine = 0.f, partner = 0.f;
+            // thread -> (row of the pass, batch column, share of the warps); the shares meet through shuffles
+            constexpr int kShares = kRowLanes / 8;
+            const int r32 = tid / kRowLanes, b = (tid % kRowLanes) / kShares, h = tid % kShares;
+            const int tile = r32 >> 4, r = r32 & 15;
+            const int v = row0 + r32;
+            const int bb = b < P.B ? b : 0;
+            // element of the partial-sum block of a (warp, tile): row pair r & 7, lane t = b / 2, value (r / 8) * 2 + (b & 1)
+            const int fe = (r >> 3) * 2 + (bb & 1);
+            const int fl = ((r & 7) * tcols + (bb >> 1)) * 4 + fe;
+            const int pl = (((r ^ 1) & 7) * tcols + (bb >> 1)) * 4 + fe;
+            const int wstride = 2 * 8 * tcols * 4;
+            const float* ared = myred + tile * 8 * tcols * 4 + h * (kWarps / kShares) * wstride;
+            const float* cred = myred + acc_floats + (h * (kWarps / kShares) * 32 + r32) * P.B + bb;
+            float mine = 0.f, partner = 0.f, cm = 0.f, cp = 0.f;
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
-                mine += myred[((w * 2 + tile) * 32 + fl) * 4 + fe];
-                partner += myred[((w * 2 + tile) * 32 + pl) * 4 + fe];
+            for (int w = 0; w < kWarps / kShares; ++w) {
+                mine += ared[w * wstride + fl];
+                cm += cred[w * 32 * P.B];
             }
-            if (tile < ntile && v < row_end && b < P.B && !failed) {
+            mine -= cm;
+#pragma unroll
+            for (int o = 1; o < kShares; o <<= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+            mine *= F::kInvUnit;
+            if (P.mode != CB_MODE_GEMV) {
+                const float* pred = myred + acc_floats + (h * (kWarps / kShares) * 32 + (r32 ^ 1)) * P.B + bb;
+#pragma unroll
+                for (int w = 0; w < kWarps / kShares; ++w) {
+                    partner += ared[w * wstride + pl];
+                    cp += pred[w * 32 * P.B];
+                }
+                partner -= cp;
+#pragma unroll
+                for (int o = 1; o < kShares; o <<= 1) partner += __shfl_xor_sync(0xffffffffu, partner, o);
+                partner *= F::kInvUnit;
+            }
+            const bool store = h == 0 && tile < ntile && v < row_end && b < P.B && !failed;
+            if (store) {
                 if (P.split_k == 1) epilogue<OutT>(P, b, v, mine, partner);
                 else P.partial[((size_t)split * P.B + b) * P.V + v] = mine;
             }
         }
     }
-    CB_STAMP(6);
     if (failed) atomicExch(&g_stream_status, failed);
 
     if (P.split_k > 1) {
@@ -370,11 +559,76 @@ gemv_stream_kernel(const __half* __restrict__ x, const StreamParams S) {
             if (tid == 0) P.counters[slab] = 0;
         }
     }
+    // A free launch did not wait for its predecessor: its first CTA does so before it exits, so that this grid never
+    // completes before the grid it was issued after.
+    if (S.launch_kind == kLaunchFree && blockIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
     peer_signal(P, peer_epoch);
 }
 
-template <int BITS, bool BF>
-int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, size_t scratch_bytes,
+// ---- chains: which launches of a capture follow one another directly, and what they touch (host side) --------------
+struct ChainKey {
+    unsigned long long capture;
+    cudaStream_t stream;
+    bool operator<(const ChainKey& o) const { return capture != o.capture ? capture < o.capture : stream < o.stream; }
+};
+struct Range {
+    uintptr_t lo, hi;
+    bool overlaps(const Range& o) const { return lo < o.hi && o.lo < hi; }
+};
+struct LaunchRec {
+    Range in;              // activations
+    Range out[3];          // outputs
+    int nout;
+    bool scratch;          // Split-K partial sums and counters
+    bool exclusive;        // rank hand-shake or peer stores: ordered after everything, and everything after it
+};
+constexpr int kMaxUnordered = 32;    // launches a chain may run without an ordered one in between
+struct ChainState {
+    cudaGraphNode_t last;              // the node of this library's latest launch on (capture, stream)
+    int count;                         // launches since (and including) the last ordered one
+    LaunchRec recs[kMaxUnordered];     // their operands: what a new launch must not overlap to run free
+};
+std::mutex g_chain_mutex;
+std::map<ChainKey, ChainState> g_chains;
+long long g_chain_counts[4] = {0, 0, 0, 0};    // chain heads, followers, followers that are ordered, followers that run free
+
+// The stream's capture state: true and (id, the single node the next launch will depend on) when a capture is active.
+bool capture_tail(cudaStream_t stream, unsigned long long* id, cudaGraphNode_t* tail) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    const cudaGraphNode_t* deps = nullptr;
+    const cudaGraphEdgeData* edges = nullptr;
+    size_t ndeps = 0;
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamGetCaptureInfo_v3(stream, &st, id, &graph, &deps, &edges, &ndeps) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    if (st != cudaStreamCaptureStatusActive) return false;
+    *tail = (ndeps == 1 && deps != nullptr) ? deps[0] : nullptr;
+    return true;
+}
+
+// Does launch `a` read what launch `b` (issued earlier) wrote?
+bool reads_from(const LaunchRec& a, const LaunchRec& b) {
+    if (a.exclusive || b.exclusive || (a.scratch && b.scratch)) return true;
+    for (int k = 0; k < b.nout; ++k)
+        if (a.in.overlaps(b.out[k])) return true;
+    return false;
+}
+
+// Does launch `a` have to be ordered after launch `b` (issued earlier)?
+bool conflicts(const LaunchRec& a, const LaunchRec& b) {
+    if (reads_from(a, b)) return true;                                                    // read after write
+    for (int m = 0; m < a.nout; ++m) {
+        if (a.out[m].overlaps(b.in)) return true;                                         // write after read
+        for (int k = 0; k < b.nout; ++k)
+            if (a.out[m].overlaps(b.out[k])) return true;                                 // write after write
+    }
+    return false;
+}
+
+template <int BITS, int KIND>
+int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, void* scratch, size_t scratch_bytes,
              cudaStream_t stream) {
     const int sms = sm_count_current();
     if (sms <= 0) return CB_ERR_CUDA;
@@ -390,29 +644,31 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
         meta += ((4 - meta) % 128 + 128) % 128;                        // rows 4 bytes apart (mod 128): conflict-free 2-byte reads
         int pitch = ng * group_bytes;
         pitch += ((group_bytes - pitch) % 128 + 128) % 128;           // pitch == group_bytes (mod 128): conflict-free fragment reads
-        int xb = ng * 256;
-        xb += ((64 - xb) % 128 + 128) % 128;                          // batch rows 64 bytes apart (mod 128)
         size_t off = 0;
-        out.off_bar = (unsigned)off; off += 64;                      // one mbarrier per ring slot, at most 8 slots
+        out.off_bar = (unsigned)off; off += 128;                     // one mbarrier per ring slot (at most 8), then 64 zero bytes
         off = (off + 127) & ~(size_t)127;
-        out.off_red = (unsigned)off; off += (size_t)2 * kWarps * 2 * 32 * 4 * sizeof(float);
-        out.off_x = 0;
+        out.off_red = (unsigned)off; off += (size_t)2 * (kWarps * 2 * 8 * ((P.B + 1) / 2) * 4 + kWarps * 32 * P.B) * sizeof(float);
+        out.off_xsum = (unsigned)off; off += (size_t)2 * P.groups * 8 * sizeof(float);
+        off = (off + 127) & ~(size_t)127;
+        out.off_xs = (unsigned)off; off += (size_t)ng * P.B * 4 * kXBlock;   // staged activations of one partition
         off = (off + 127) & ~(size_t)127;
         out.slot_bytes = rpp * (pitch + 2 * meta);
         out.off_ring = (unsigned)off; off += (size_t)nbuf * out.slot_bytes;
-        out.pitch = pitch; out.meta_stride = meta; out.xb_stride = xb; out.nbuf = nbuf; out.rpp = rpp;
+        out.pitch = pitch; out.meta_stride = meta; out.nbuf = nbuf; out.rpp = rpp;
         return off;
     };
-    const int vpairs = (P.V + 1) / 2;
+    // slabs are whole row PAIRS (the two operands of silu(gate)*up and of a rotation are neighbouring rows)
+    const int gran = 2;
+    const int vpairs = (P.V + gran - 1) / gran;
     // Slabs, passes and ring depth of a candidate (CTAs, split, rows per pass) under a shared-memory cap.
     struct Plan { int split, rpp, nbuf, nslabs, npass; bool ok; };
     auto plan = [&](int ctas, int sp, int rpp, size_t cap) -> Plan {
         Plan pl{sp, rpp, 0, 0, 0, false};
         StreamParams tmp{};
         if (layout(sp, 1, rpp, tmp) > cap) return pl;
-        int nslabs = std::max(1, std::min(ctas / sp, (vpairs + 7) / 8));          // at least 16 rows per slab when possible
+        int nslabs = std::max(1, std::min(ctas / sp, (gran * vpairs + 15) / 16));          // at least 16 rows per slab when possible
         nslabs = std::min(nslabs, vpairs);
-        const int rows_per_slab = 2 * ((vpairs + nslabs - 1) / nslabs);
+        const int rows_per_slab = gran * ((vpairs + nslabs - 1) / nslabs);
         pl.nslabs = nslabs;
         pl.npass = (rows_per_slab + rpp - 1) / rpp;
         pl.nbuf = std::min(pl.npass, kMaxBuf);
@@ -428,7 +684,7 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
     const int per_sm = rho <= 0 ? 2 : (int)std::min<int64_t>(std::max<int64_t>(rho, 2), 4);
     Plan pick{};
     {
-        const Plan c = plan(sms, split, 32, kSmemCap);
+        const Plan c = plan(sms, split, 32, kSmemCapTwo);
         if (rho > 0 && rho <= 2 && c.ok && c.npass == 1) pick = c;
     }
     if (!pick.ok) {
@@ -458,16 +714,15 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
     }
     const size_t smem = layout(split, pick.nbuf, pick.rpp, S);
     P.split_k = split;
-#ifdef CB_STREAM_DEBUG
-    { const char* e = getenv("CB_GEMV_DEBUG"); S.dbg = e ? atoi(e) : 0; }
-#endif
     S.g = P;
     S.nslabs = nslabs;
+    S.row_gran = gran;
     S.pair_q = vpairs / nslabs; S.pair_r = vpairs % nslabs;
     S.grp_q = gpairs / split; S.grp_r = gpairs % split;
+    const unsigned int grid = (unsigned)(nslabs * split);
 
     static bool attr_done[64] = {};     // per device: the opt-in to large dynamic shared memory
-    auto kern = gemv_stream_kernel<BITS, BF>;
+    auto kern = gemv_stream_kernel<BITS, KIND>;
     int dev = 0;
     CB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
@@ -477,8 +732,41 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
         CB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
+
+    // Kind of this launch.  Inside stream capture: a follower if the capture's tail is this library's previous launch
+    // on this stream, else the head of a new chain (ordered).  A follower runs free if its operands overlap those of
+    // no launch since the chain's last ordered one, and that was at most kMaxUnordered - 1 launches ago.
+    ChainKey key{0ull, stream};
+    cudaGraphNode_t tail = nullptr;
+    const bool in_chain = pdl && chains && capture_tail(stream, &key.capture, &tail);
+    std::unique_lock<std::mutex> lock(g_chain_mutex, std::defer_lock);
+    LaunchRec rec{};
+    S.launch_kind = kLaunchPlain;
+    bool follower = false;
+    if (in_chain) {
+        lock.lock();
+        if (g_chains.size() > 4096) g_chains.clear();      // forgotten chains only mean that their next launch is a head
+        auto it = g_chains.find(key);
+        follower = it != g_chains.end() && tail != nullptr && it->second.last == tail;
+        const size_t esz = 2;
+        rec.in = Range{reinterpret_cast<uintptr_t>(x), reinterpret_cast<uintptr_t>(x) + (size_t)P.B * P.K * esz};
+        rec.nout = P.mode == CB_MODE_QKV ? 3 : 1;
+        for (int k = 0; k < rec.nout; ++k) {
+            const uintptr_t o = reinterpret_cast<uintptr_t>(P.p[k].out);
+            rec.out[k] = Range{o, o + (size_t)P.B * P.p[k].n * esz};
+        }
+        rec.scratch = split > 1;
+        rec.exclusive = P.sync.on != 0 || P.n_peers > 0;
+        bool free_run = follower && it->second.count < kMaxUnordered;
+        if (free_run)
+            for (int j = 0; j < it->second.count && free_run; ++j)
+                if (conflicts(rec, it->second.recs[j])) free_run = false;
+        S.launch_kind = free_run ? kLaunchFree : kLaunchOrdered;
+        ++g_chain_counts[follower ? 1 : 0];
+        if (follower) ++g_chain_counts[free_run ? 3 : 2];
+    }
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)(nslabs * split));
+    cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -487,29 +775,47 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, void* scratch, 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = pdl ? 1 : 0;
-    CB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, reinterpret_cast<const __half*>(x), S));
+    CB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, reinterpret_cast<const unsigned char*>(x), S));
+    if (in_chain) {
+        unsigned long long id = 0;
+        cudaGraphNode_t node = nullptr;
+        if (capture_tail(stream, &id, &node) && id == key.capture && node != nullptr) {
+            ChainState& cs = g_chains[key];
+            cs.last = node;
+            if (S.launch_kind == kLaunchOrdered) cs.count = 0;      // everything before an ordered launch is done when its successors start
+            cs.recs[cs.count++] = rec;
+        } else {
+            g_chains.erase(key);
+        }
+    }
     return CB_OK;
 }
 
 }  // namespace
 
 // Returns CB_OK after launching, a CB_ERR_* code on a CUDA error, or -1 when this problem is outside
-// the kernel's domain (the caller then uses the generic kernel).
-int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, int64_t rho, bool pdl,
-                       void* scratch, size_t scratch_bytes, cudaStream_t stream) {
+// the kernel's domain (the caller then uses the generic kernel).  `operands`: 0 = fp16 subnormal form, 1 = fp16
+// with the 1024 offset (A/B checks); bf16 always uses its 128-offset form.
+int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, int64_t rho, bool pdl, bool chains,
+                       int operands, void* scratch, size_t scratch_bytes, cudaStream_t stream) {
     if ((dtype != CB_F16 && dtype != CB_BF16) || P.group_size != 128 || P.K % 256 != 0 || P.B > kMaxBatchBlock || P.B < 1) return -1;
     if (reinterpret_cast<uintptr_t>(x) % 16 != 0) return -1;
     for (int i = 0; i < 3; ++i)
         if (reinterpret_cast<uintptr_t>(P.p[i].w) % 16 != 0) return -1;
     if ((P.mode != CB_MODE_GEMV) && (P.V & 1)) return -1;
-    switch (bits) {
-        case 2: return dtype == CB_BF16 ? launch_t<2, true>(x, P, rho, pdl, scratch, scratch_bytes, stream)
-                                        : launch_t<2, false>(x, P, rho, pdl, scratch, scratch_bytes, stream);
-        case 3: return dtype == CB_BF16 ? launch_t<3, true>(x, P, rho, pdl, scratch, scratch_bytes, stream)
-                                        : launch_t<3, false>(x, P, rho, pdl, scratch, scratch_bytes, stream);
-        default: return dtype == CB_BF16 ? launch_t<4, true>(x, P, rho, pdl, scratch, scratch_bytes, stream)
-                                         : launch_t<4, false>(x, P, rho, pdl, scratch, scratch_bytes, stream);
-    }
+    const int kind = dtype == CB_BF16 ? kFragMagicB : (operands == 1 ? kFragMagicH : kFragSubnormal);
+#define CB_STREAM_CASE(B_, K_) \
+    if (bits == B_ && kind == K_) return launch_t<B_, K_>(x, P, rho, pdl, chains, scratch, scratch_bytes, stream);
+    CB_STREAM_CASE(2, kFragSubnormal) CB_STREAM_CASE(3, kFragSubnormal) CB_STREAM_CASE(4, kFragSubnormal)
+    CB_STREAM_CASE(2, kFragMagicH) CB_STREAM_CASE(3, kFragMagicH) CB_STREAM_CASE(4, kFragMagicH)
+    CB_STREAM_CASE(2, kFragMagicB) CB_STREAM_CASE(3, kFragMagicB) CB_STREAM_CASE(4, kFragMagicB)
+#undef CB_STREAM_CASE
+    return -1;
+}
+
+void chain_stats(long long* out4) {
+    std::lock_guard<std::mutex> lock(g_chain_mutex);
+    for (int i = 0; i < 4; ++i) out4[i] = g_chain_counts[i];
 }
 
 int stream_status_read_and_clear(int* out) {
@@ -520,13 +826,6 @@ int stream_status_read_and_clear(int* out) {
     return CB_OK;
 }
 
-#ifdef CB_STREAM_TIMING
-}  // namespace cb
-extern "C" int cb_debug_stream_times(unsigned long long* host, int ctas) {
-    return (int)cudaMemcpyFromSymbol(host, cb::g_stream_times, sizeof(unsigned long long) * 8 * ctas);
-}
-namespace cb {
-#endif
 
 int occupancy_gemv_stream(int bits) {
     (void)bits;

@@ -9,7 +9,8 @@
 // The array below is a file-scope __device__ object: every GPU that loads the library holds
 // kStaticScratchBytes of it until the process exits.  In host code its NAME is only a handle; the
 // device address is obtained once per device with cudaGetSymbolAddress and that pointer is what the
-// kernel receives.
+// kernel receives.  The address is remembered for the life of the process: a caller that destroys the
+// device's primary context (cudaDeviceReset) must not use this entry point afterwards.
 #include <mutex>
 
 #include "cb_common.cuh"
@@ -63,6 +64,12 @@ int cb_packed_gemv_static_scratch(const void* x, int64_t B, const cb_weight* w, 
     }
     const int64_t nchunks = (K + 31) / 32;
     const int64_t pk = split_k < nchunks ? split_k : nchunks;
+    const int64_t tiles = ((B + kMaxBatchBlock - 1) / kMaxBatchBlock) * ((w->n + kTileN - 1) / kTileN);
+    if (pk > 1 && tiles > 65536) {
+        set_error("packed_gemv_static_scratch: ceil(B/8)*ceil(N/16) = %lld exceeds the 65536 arrival counters of the "
+                  "built-in array; call with split_k = 1 or use cb_packed_gemv", (long long)tiles);
+        return CB_ERR_INVALID;
+    }
     const size_t need = cb_gemv_scratch_bytes(B, w->n, pk);
     if (need > kStaticScratchBytes) {
         set_error("packed_gemv_static_scratch: split_k=%lld x batch=%lld x rows=%lld needs %zu bytes of scratch; the "

@@ -30,6 +30,16 @@ int cbo_num_threads(void) {
 #endif
 }
 
+/* Threads the parallel loops below use from now on (a launcher such as torchrun exports OMP_NUM_THREADS=1, which
+ * would otherwise make the timed CPU baseline single-threaded). */
+void cbo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* Code k of a row: bits [k*bits, k*bits+bits) of the row's little-endian stream of 32-bit words
  * (crispybits_kernels/reference.py:58-67; csrc/bitpack.cuh:10-18). */
 static inline uint32_t code_at(const uint32_t* row, int64_t k, int bits) {

@@ -55,6 +55,16 @@ def num_threads() -> int:
     return int(lib().cbo_num_threads())
 
 
+def use_all_host_threads() -> int:
+    """Make the OpenMP loops use every core this process may run on, whatever OMP_NUM_THREADS says."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    L = lib()
+    L.cbo_set_num_threads.argtypes = [_int]
+    L.cbo_set_num_threads.restype = None
+    L.cbo_set_num_threads(n)
+    return num_threads()
+
+
 def _f(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 

@@ -1,7 +1,6 @@
 """The decode stack (packed linears of N transformer blocks, column-parallel over ranks).
 
-CPU tests: the torch quantise+pack used to synthesise weights is bit-identical to the oracle; the
-sharding arithmetic and the 2-rank gather (gloo) reproduce the 1-rank result with the oracle standing
+CPU tests: the sharding arithmetic and the 2-rank gather (gloo) reproduce the 1-rank result with the oracle standing
 in for the kernels.  GPU test: the stack on one GPU against the fp32 evaluation of the same data flow.
 """
 import os
@@ -15,17 +14,14 @@ import torch
 from conftest import PKG, ROOT
 
 
-@pytest.mark.parametrize("bits", [2, 3, 4])
-@pytest.mark.parametrize("n,k,gs", [(24, 256, 128), (19, 200, 128), (16, 640, 64), (5, 32, 32)])
-def test_torch_quantize_pack_is_bit_identical_to_the_oracle(bits, n, k, gs):
-    from crispybits_kernels.stack import quantize_pack
+def oracle_packer(w, bits, group_size=128, dtype=torch.float16):
+    """The CPU oracle's quantise + pack as a DecodeStack packer (test infrastructure)."""
+    from crispybits_kernels import PackedLinearWeight
     from oracle import cb_oracle as O
-    w = torch.randn(n, k, generator=torch.Generator().manual_seed(bits * 100 + n)) * 0.02
-    got = quantize_pack(w, bits, gs)
-    want = O.pack_linear_dict(w.numpy(), bits, gs, None, "float16")
-    assert np.array_equal(got.packed.numpy(), want["packed"])
-    assert np.array_equal(got.scales.float().numpy(), want["scales"])
-    assert np.array_equal(got.zeros.float().numpy(), want["zeros"])
+    d = O.pack_linear_dict(w.float().cpu().numpy(), bits, group_size, None, "float16")
+    t = lambda a: torch.from_numpy(a).to(w.device)
+    return PackedLinearWeight(t(d["packed"]), t(d["scales"]).to(dtype), t(d["zeros"]).to(dtype), bits, group_size,
+                              w.shape[1], w.shape[0])
 
 
 def test_bitmap_draw_is_the_reference_draw():
@@ -47,10 +43,11 @@ def _worker(rank, world, port, out_path):
     ops.set_backend(oracle_backend)
     torch.manual_seed(0)
     x = torch.randn(2, 256).half()
-    sharded = DecodeStack(2, 256, 512, bitmap=[3, 4], rank=rank, world=world, device="cpu", std=0.05)
+    from test_stack import oracle_packer
+    sharded = DecodeStack(2, 256, 512, bitmap=[3, 4], rank=rank, world=world, device="cpu", std=0.05, packer=oracle_packer)
     y = sharded.step(x)
     if rank == 0:
-        full = DecodeStack(2, 256, 512, bitmap=[3, 4], rank=0, world=1, device="cpu", std=0.05)
+        full = DecodeStack(2, 256, 512, bitmap=[3, 4], rank=0, world=1, device="cpu", std=0.05, packer=oracle_packer)
         torch.save({"sharded": y, "full": full.step(x), "bytes": (sharded.algorithmic_bytes(2), full.algorithmic_bytes(2))},
                    out_path)
     dist.barrier()
@@ -76,7 +73,7 @@ def test_two_rank_column_split_matches_one_rank(tmp_path):
 @pytest.mark.gpu
 def test_stack_on_gpu_matches_fp32_dataflow():
     from crispybits_kernels import ops
-    from crispybits_kernels.stack import DecodeStack, quantize_pack
+    from crispybits_kernels.stack import DecodeStack
     from oracle import cb_oracle as O
     ops.set_backend("cuda")
     st = DecodeStack(3, 512, 1024, bitmap=[4, 2, 3], device="cuda", std=0.05)

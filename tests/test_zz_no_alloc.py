@@ -86,3 +86,39 @@ def test_static_scratch_without_split_and_limits():
     assert rc == 0, lib.cb_last_error()
     torch.cuda.synchronize()
     assert rel_err(out8, ref_linear(x8, wd)) < 2e-3
+
+
+@pytest.mark.parametrize("dtype,gs", [(torch.float32, 128), (torch.float16, 64)])
+def test_static_scratch_split_k_through_the_generic_kernel_twice(dtype, gs):
+    """fp32 activations, or a group size other than 128, take the shape-generic decode kernel: its Split-K partial
+    sums and arrival counters then live in the library's array.  Two calls in a row, against the ordinary entry point
+    with the caller's own buffer."""
+    _C, lib = _lib()
+    n, k, B, split_k, bits = 520, 1024, 2, 5, 3
+    w, wd, bd = make(n, k, bits, dtype, DEV, bias=True, seed=91, gs=gs)
+    rec = _C._Weight(w.packed.data_ptr(), w.scales.data_ptr(), w.zeros.data_ptr(), w.bias.data_ptr(), n)
+    stream = torch.cuda.current_stream().cuda_stream
+    own = torch.zeros(lib.cb_gemv_scratch_bytes(B, n, split_k), dtype=torch.uint8, device=DEV)
+    code = {torch.float32: 0, torch.float16: 1}[dtype]
+    gen = torch.Generator(DEV).manual_seed(5)
+    for call in range(2):
+        x = torch.randn(B, k, device=DEV, dtype=dtype, generator=gen)
+        want = torch.empty(B, n, device=DEV, dtype=dtype)
+        got = torch.full((B, n), float("nan"), device=DEV, dtype=dtype)
+        rc = lib.cb_packed_gemv(x.data_ptr(), B, ctypes.byref(rec), want.data_ptr(), k, bits, gs, code, split_k, 1, 0,
+                                own.data_ptr(), own.numel(), stream)
+        assert rc == 0, lib.cb_last_error()
+        rc = lib.cb_packed_gemv_static_scratch(x.data_ptr(), B, ctypes.byref(rec), got.data_ptr(), k, bits, gs, code,
+                                               split_k, 1, 0, stream)
+        assert rc == 0, lib.cb_last_error()
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"call {call}"          # same kernel, same split order
+        assert rel_err(got, ref_linear(x, wd, bd)) < (1e-4 if dtype == torch.float32 else 2e-3), f"call {call}"
+
+
+def test_static_scratch_refuses_more_tiles_than_counters():
+    _C, lib = _lib()
+    # ceil(N/16) > 65536 with a K split: documented as CB_ERR_INVALID (nothing is launched, pointers are not read)
+    rec = _C._Weight(16, 16, 16, 0, 16 * 65536 + 16)
+    rc = lib.cb_packed_gemv_static_scratch(16, 1, ctypes.byref(rec), 16, 64, 4, 32, 1, 2, 1, 0, None)
+    assert rc == 1 and b"arrival counters" in lib.cb_last_error()
