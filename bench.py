@@ -320,6 +320,23 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
         gbs = gemv_bytes(N_OUT, K_IN, b) / (us * 1e-6) / 1e9
         gemv[f"w{b}"] = {"us": us, "gbs": gbs, "frac_of_hbm_peak": gbs / hbm_peak,
                          "split_k": ops._resolve(None, 1, 1, N_OUT, K_IN, torch.device(device), torch.float16, GROUP)}
+    # The same launches as a chain in which every launch reads the previous launch's output (what consecutive layers of a
+    # decode step do): each launch then waits for its predecessor's completion.
+    dep_graphs = []
+    for b in BITS:
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            cur, keep = x, []
+            for w in weights[b]:
+                cur = ck.packed_linear(cur, w, workspace=ws)
+                keep.append(cur)
+        dep_graphs.append((gr, keep))
+    dep_ms, _ = timed_graph_replays([g_ for g_, _ in dep_graphs], args.steps, 3, barrier)
+    for b, ms in zip(BITS, dep_ms):
+        us = reduce_max(ms) * 1e3 / (args.steps * COPIES)
+        gbs = gemv_bytes(N_OUT, K_IN, b) / (us * 1e-6) / 1e9
+        gemv[f"w{b}"]["dependent_chain"] = {"us": us, "gbs": gbs, "frac_of_hbm_peak": gbs / hbm_peak}
+    del dep_graphs
     top = gemv["w4"]
     roofline = {"bound": "hbm", "achieved": top["gbs"], "peak": hbm_peak, "unit": "GB/s",
                 "frac": top["gbs"] / hbm_peak, "traffic": NCU_TRAFFIC_W4, "kernel": "decode GEMV W4 4096x4096 b1",
@@ -447,6 +464,15 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
         extra["fused_decode"] = bench_fused_decode(device, hbm_peak, peak_kind)
     if rank == 0 and not args.no_gemm:
         extra["gemm"] = bench_gemm(device, tf_peak, peak_kind)
+    if rank == 0 and not args.no_sweeps:
+        try:
+            rc = bench_reference_cuda(device, hbm_peak, tf_peak)
+        except Exception as exc:      # the reference's kernels are a comparison, not a dependency of this line
+            rc = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+            torch.cuda.synchronize()
+        extra["reference_cuda"] = rc if rc is not None else {"unavailable": "oracle/_ref/crispybits_ref_C.so is not built (python oracle/build_ref_cuda.py)"}
+        if isinstance(rc, dict) and "gemv_w4_4096x4096_b1" in rc:
+            extra["speedup_vs_reference_cuda"] = {f"gemv_w{b}": round(rc[f"gemv_w{b}_4096x4096_b1"]["us"] / gemv[f"w{b}"]["us"], 2) for b in BITS}
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         v, per, threads, sample = cpu_gemv_sample()
@@ -459,7 +485,8 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
         "config": {"workload": "gemv_4096x4096_w4_w3_w2_b1", "group_size": GROUP, "copies_per_bits": COPIES,
                    "l2": f"inputs larger than L2: each step streams {step_bytes / 1e6:.0f} MB of distinct weights "
                          f"(126 MB L2)", "launch": "CUDA graph replay, one graph per bit-width; the calls of a graph "
-                         "read the same x and write their own outputs",
+                         "read the same x and write their own outputs, so inside the captured chain they overlap "
+                         "(gemv.wN.dependent_chain: the same launches with each one reading its predecessor's output)",
                    "multi_gpu": "independent replicas (single matmuls stay on one GPU)" if world > 1 else "n/a"},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gemv": gemv, "clocks": clocks,
         "gpu_launches": args.steps * 3 * COPIES, **extra,
@@ -664,15 +691,15 @@ def _graph_timed_us(call, iters):
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            for i in range(iters):
-                call(i)
+            keep = [call(i) for i in range(iters)]      # every call keeps its own outputs, as the calls of a model do
         replay = g.replay
     except Exception as exc:
         print(f"[bench] gemm graph capture failed: {type(exc).__name__}: {exc}", file=sys.stderr)
         torch.cuda.synchronize()
-    reps = 3
+    reps = 5
     if replay is not None:
-        replay()
+        for _ in range(2):
+            replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -722,7 +749,8 @@ def bench_gemv_sweep(device, hbm_peak, peak_kind, iters_per_graph=1):
             for batch in (1, 2, 4, 8):
                 x = torch.randn(batch, k, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(batch))
                 err = _gate(f"gemv w{b} {n}x{k} b{batch}", ck.packed_linear(x, ws[0], decode_threshold=8), x.float() @ wd.T)
-                us = _graph_timed_us(lambda i: ck.packed_linear(x, ws[i % len(ws)], decode_threshold=8), len(ws))
+                us = _graph_timed_us(lambda i: ck.packed_linear(x, ws[i % len(ws)], decode_threshold=8),
+                                     len(ws) * -(-96 // len(ws)))       # about a hundred launches per graph
                 gbs = gemv_bytes(n, k, b, batch) / (us * 1e-6) / 1e9
                 out[f"w{b}_{n}x{k}_b{batch}"] = {"us": round(us, 3), "gbs": round(gbs, 1), "frac": round(gbs / hbm_peak, 4),
                                                  "err": float(f"{err:.2e}")}
@@ -757,10 +785,10 @@ def bench_fused_decode(device, hbm_peak, peak_kind):
     for o, r, nm in zip(ck.fused_qkv(x, *sets[0]), refs, "qkv"):
         _gate(f"fused_qkv {nm}", o, r)
     nbytes = gemv_bytes(12288, k, b)
-    out["qkv_12288x4096_w3_fused_api"] = entry(_graph_timed_us(lambda i: ck.fused_qkv(x, *sets[i % ncopy]), ncopy), nbytes)
+    out["qkv_12288x4096_w3_fused_api"] = entry(_graph_timed_us(lambda i: ck.fused_qkv(x, *sets[i % ncopy]), ncopy * -(-48 // ncopy)), nbytes)
     cats = [cat(st) for st in sets]
     _gate("concatenated qkv", ck.packed_linear(x, cats[0]), torch.cat(refs, 1))
-    out["qkv_12288x4096_w3_concatenated"] = entry(_graph_timed_us(lambda i: ck.packed_linear(x, cats[i % ncopy]), ncopy), nbytes)
+    out["qkv_12288x4096_w3_concatenated"] = entry(_graph_timed_us(lambda i: ck.packed_linear(x, cats[i % ncopy]), ncopy * -(-48 // ncopy)), nbytes)
     del sets, cats, refs
     torch.cuda.empty_cache()
     # gate/up: 2 x (11008, 4096), seeds 5, 6
@@ -769,13 +797,58 @@ def bench_fused_decode(device, hbm_peak, peak_kind):
     sets = list(zip(*[device_copies(d, device, ncopy) for d in dg]))
     rg, ru = (x.float() @ torch.from_numpy(_oracle_dequant(d)).to(device).T for d in dg)
     _gate("fused_gate_up", ck.fused_gate_up(x, *sets[0]), torch.nn.functional.silu(rg) * ru)
-    out["gate_up_2x11008x4096_w3_fused_api"] = entry(_graph_timed_us(lambda i: ck.fused_gate_up(x, *sets[i % ncopy]), ncopy),
+    out["gate_up_2x11008x4096_w3_fused_api"] = entry(_graph_timed_us(lambda i: ck.fused_gate_up(x, *sets[i % ncopy]), ncopy * -(-48 // ncopy)),
                                                      2 * gemv_bytes(11008, k, b) - k * 2 - 11008 * 2)
     cats = [cat(st) for st in sets]
     _gate("concatenated gate/up", ck.packed_linear(x, cats[0]), torch.cat([rg, ru], 1))
-    out["gate_up_22016x4096_w3_concatenated"] = entry(_graph_timed_us(lambda i: ck.packed_linear(x, cats[i % ncopy]), ncopy),
+    out["gate_up_22016x4096_w3_concatenated"] = entry(_graph_timed_us(lambda i: ck.packed_linear(x, cats[i % ncopy]), ncopy * -(-48 // ncopy)),
                                                       gemv_bytes(22016, k, b))
     out["note"] = f"fraction of the HBM copy peak {hbm_peak:.0f} GB/s ({peak_kind}); L2-cold as the sweep"
+    return out
+
+
+def bench_reference_cuda(device, hbm_peak, tf_peak):
+    """The reference's OWN CUDA kernels (Crispybits/Kernel/csrc/packed_gemv.cu, packed_gemm.cu, compiled unmodified for
+    sm_100a by oracle/build_ref_cuda.py) timed on this GPU with the harness used for this library: the 4096x4096 batch-1
+    GEMV at W4/W3/W2 (L2-cold, captured back to back) with the reference's Split-K rule and with split_k = 1, and the
+    M = 1024 prefill GEMM.  None when the module has not been built."""
+    from oracle import build_ref_cuda
+    ref = build_ref_cuda.load_module()
+    if ref is None:
+        return None
+    out = {}
+    e16 = torch.empty(0, device=device, dtype=torch.float16)
+    sms, bn = int(ref.sm_count()), int(ref.tile_n())
+    for b in BITS:
+        d = synth_weight_numpy(b, b)
+        ws = device_copies(d, device, _copies_beyond_l2(gemv_bytes(N_OUT, K_IN, b)))
+        wd = torch.from_numpy(_oracle_dequant(d)).to(device)
+        x = torch.randn(1, K_IN, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(1))
+        wsp = torch.zeros(2, dtype=torch.int32, device=device)
+        tiles = -(-N_OUT // bn)
+        rule = 1 if tiles >= sms else -(-sms // tiles)          # SM-underfill rule, rho = 1 (ops.py:144-153 of the reference)
+        best = None
+        for split in sorted({1, rule}):
+            call = lambda i, split=split: ref.packed_gemv(x, ws[i % len(ws)].packed, ws[i % len(ws)].scales, ws[i % len(ws)].zeros,
+                                                           e16, b, K_IN, GROUP, split, 1, 0, wsp)
+            _gate(f"reference CUDA gemv w{b} split_k={split}", call(0), x.float() @ wd.T, 3e-3)
+            us = _graph_timed_us(call, len(ws) * -(-96 // len(ws)))
+            if best is None or us < best[0]:
+                best = (us, split)
+        gbs = gemv_bytes(N_OUT, K_IN, b) / (best[0] * 1e-6) / 1e9
+        out[f"gemv_w{b}_4096x4096_b1"] = {"us": round(best[0], 3), "gbs": round(gbs, 1), "frac": round(gbs / hbm_peak, 4),
+                                          "split_k": best[1], "rule_split_k": rule}
+        if b != 2:
+            xm = torch.randn(1024, K_IN, device=device, dtype=torch.float16, generator=torch.Generator(device).manual_seed(6))
+            call = lambda i: ref.packed_gemm(xm, ws[i % 2].packed, ws[i % 2].scales, ws[i % 2].zeros, e16, b, K_IN, GROUP, 0, True)
+            _gate(f"reference CUDA gemm w{b}", call(0)[:256], xm[:256].float() @ wd.T, 3e-3)
+            us = _graph_timed_us(call, 4)
+            tf = 2.0 * 1024 * N_OUT * K_IN / (us * 1e-6) / 1e12
+            out[f"gemm_m1024_4096x4096_w{b}"] = {"us": round(us, 2), "tflops": round(tf, 1), "frac_of_dense_peak": round(tf / tf_peak, 4)}
+        del ws, wd
+        torch.cuda.empty_cache()
+    out["note"] = ("the reference's CUDA extension built unmodified for sm_100a and run on this GPU; same inputs, same CUDA-graph "
+                   "timing as this library's figures; GEMV: the faster of the reference's Split-K rule and split_k = 1")
     return out
 
 

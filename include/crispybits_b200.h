@@ -152,6 +152,20 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out,
                    int64_t K, int bits, int64_t group_size, int dtype,
                    int act, int use_tensor_cores, void* stream);
 
+/* cb_packed_gemm with caller-provided scratch, which lets the tcgen05 kernel split K where the output tiles alone
+ * would leave more than half of the SMs idle (few tokens against a narrow matrix: M <= 512 at N = 4096 on 148 SMs).
+ * The K ranges store fp32 partial sums [splits, M, n] into `scratch` (16-byte aligned, cb_gemm_scratch_bytes() bytes;
+ * its contents need no initialisation and are garbage afterwards) and a second small kernel adds them in range order,
+ * applies bias and activation and rounds once: deterministic, same tolerance as the unsplit kernel.  With scratch ==
+ * NULL, or where no split applies, this is cb_packed_gemm.  The reference covers every M with one grid rule
+ * (Crispybits/Kernel/csrc/packed_gemm.cu:158-179) and has no counterpart of the split. */
+int cb_packed_gemm_scratch(const void* x, int64_t M, const cb_weight* w, void* out,
+                           int64_t K, int bits, int64_t group_size, int dtype,
+                           int act, int use_tensor_cores, void* scratch, size_t scratch_bytes, void* stream);
+
+/* Bytes of scratch cb_packed_gemm_scratch wants for [M, K] x [n, K]^T on the current device (0: it would not split). */
+size_t cb_gemm_scratch_bytes(int64_t M, int64_t n, int64_t K);
+
 /* Fused prefill gate/up  out[M,n] = silu(x Wg^T) * (x Wu^T)  in one tcgen05 launch (gate and up rows share a
  * tile as neighbouring tensor-memory lanes).  The reference runs two GEMMs and an elementwise product here
  * (Crispybits/Kernel/crispybits_kernels/ops.py:216-220).  Returns CB_ERR_UNSUPPORTED outside the kernel's domain
@@ -237,6 +251,15 @@ void cb_set_option(int option, int value);
  * ends the chain; the next decode call starts a new one with an ordinary full dependency.  Outside capture nothing
  * of this applies, and cb_set_option(4, 0) switches it off.  No device memory is involved. */
 int cb_chain_stats(long long* counts4);
+
+/* The launch plan the ring decode kernel would use for a GEMV with batch B (1..8), V virtual output rows, reduction
+ * length K (a multiple of 256, group size 128), the caller's split_k and rho, on a GPU with `sms` multiprocessors.
+ * Pure host arithmetic: needs no GPU and launches nothing.  plan7 receives {grid, dynamic shared memory bytes,
+ * K split used, rows per pass, ring slots, passes per CTA, row slabs}.  rho = 1 asks for one CTA per SM with all of
+ * its shared memory, rho = 2 for two CTAs per SM with half each; either falls back to the other when its ring does
+ * not fit.  CB_ERR_UNSUPPORTED when the kernel does not take the problem (the call then runs the generic kernel).
+ * Stands where packed_gemv.cu:184-188 and host_utils.h:90-93 (cb_blocks) compute the grid from rho and the SM count. */
+int cb_decode_plan(int bits, int64_t B, int64_t V, int64_t K, int64_t split_k, int64_t rho, int sms, long long* plan7);
 
 /* Synchronises the device, then returns in *status the decode kernels' error word and clears it:
  * 0 = no problem; 0 < k < 1000 = in a decode kernel a shared-memory copy of pass k-1 did not arrive

@@ -45,8 +45,14 @@ _lib.cb_fused_gate_up.argtypes = [_vp, _i64, _WP, _WP, _vp, _i64, _int, _i64, _i
 _lib.cb_fused_qkv.argtypes = [_vp, _i64, _WP, _WP, _WP, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _i64,
                               _int, _i64, _i64, _vp, _sz, _vp]
 _lib.cb_packed_gemm.argtypes = [_vp, _i64, _WP, _vp, _i64, _int, _i64, _int, _int, _int, _vp]
+_lib.cb_packed_gemm_scratch.argtypes = [_vp, _i64, _WP, _vp, _i64, _int, _i64, _int, _int, _int, _vp, _sz, _vp]
+_lib.cb_packed_gemm_scratch.restype = _int
+_lib.cb_gemm_scratch_bytes.argtypes = [_i64, _i64, _i64]
+_lib.cb_gemm_scratch_bytes.restype = _sz
+_COUNTER_BYTES = 65536 * 4      # the decode kernels' arrival counters at the head of a stream's scratch buffer
 _lib.cb_unpack_codes.argtypes = [_vp, _i64, _i64, _int, _vp, _vp]
 _lib.cb_max_rho.argtypes = [_int, _int]
+_lib.cb_decode_plan.argtypes = [_int, _i64, _i64, _i64, _i64, _i64, _int, ctypes.POINTER(ctypes.c_longlong)]
 _lib.cb_set_option.argtypes = [_int, _int]
 _lib.cb_set_option.restype = None
 _lib.cb_decode_status.argtypes = [ctypes.POINTER(_int)]
@@ -211,8 +217,13 @@ def packed_gemm(x, packed, scales, zeros, bias, bits, in_features, group_size, a
         return out
     with torch.cuda.device(x.device):
         w = _weight(packed, scales, zeros, bias)
-        _rc(_lib.cb_packed_gemm(x.data_ptr(), M, ctypes.byref(w), out.data_ptr(), k, bits, gs, _DTYPE[x.dtype],
-                                act, 1 if use_tensor_cores else 0, _stream(x)))
+        st = _stream(x)
+        # scratch for a K split of few-token calls: behind the decode kernels' counter region of the stream's buffer
+        need = _lib.cb_gemm_scratch_bytes(M, n, k) if use_tensor_cores else 0
+        sc = _scratch_for(x, st, _COUNTER_BYTES + need) if need else None
+        _rc(_lib.cb_packed_gemm_scratch(x.data_ptr(), M, ctypes.byref(w), out.data_ptr(), k, bits, gs, _DTYPE[x.dtype],
+                                        act, 1 if use_tensor_cores else 0,
+                                        0 if sc is None else sc.data_ptr() + _COUNTER_BYTES, need, st))
     return out
 
 
@@ -521,6 +532,16 @@ def max_rho(bits: int, kind: str = "gemv") -> int:
     if r < 0:
         _rc(1)
     return int(r)
+
+
+def decode_plan(bits: int, batch: int, rows: int, in_features: int, split_k: int = 1, rho: int = 1, sms: int = 148):
+    """Launch plan of the ring decode kernel as a dict (host arithmetic only; no GPU needed), or None when the ring
+    kernel does not take the problem."""
+    out = (ctypes.c_longlong * 7)()
+    if _lib.cb_decode_plan(bits, batch, rows, in_features, split_k, rho, sms, out) != 0:
+        return None
+    keys = ("grid", "smem_bytes", "split_k", "rows_per_pass", "ring_slots", "passes", "row_slabs")
+    return dict(zip(keys, (int(v) for v in out)))
 
 
 def set_option(option: int, value: int) -> None:

@@ -40,6 +40,7 @@ int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, 
                        int operands, void* scratch, size_t scratch_bytes, cudaStream_t stream);
 int stream_status_read_and_clear(int* out);
 void chain_stats(long long* out4);
+bool stream_plan_query(int bits, int B, int V, int K, int split_k, int64_t rho, int sms, long long* out7);
 int launch_peer_wait(const GemvParams& P, cudaStream_t stream);
 int launch_peer_signal(const GemvParams& P, cudaStream_t stream);
 int gemm_status_read_and_clear(int* out);
@@ -50,7 +51,8 @@ int launch_gemm_ws_qkv(int dtype, const void* x, int64_t M, const cb_weight* q, 
                        void* out_q, void* out_k, void* out_v, const float* rope_cos, const float* rope_sin, int head_dim,
                        int perm_hd, int64_t K, int bits, int64_t gs, cudaStream_t stream);
 int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
-                   int64_t gs, int act, cudaStream_t stream);
+                   int64_t gs, int act, cudaStream_t stream, void* scratch, size_t scratch_bytes);
+int gemm_ws_splits(int64_t M, int64_t N, int64_t K);
 int launch_gemm_tc(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
                    int64_t gs, int act, cudaStream_t stream);
 
@@ -223,6 +225,19 @@ int cb_chain_stats(long long* counts4) {
     return CB_OK;
 }
 
+int cb_decode_plan(int bits, int64_t B, int64_t V, int64_t K, int64_t split_k, int64_t rho, int sms, long long* plan7) {
+    if (plan7 == nullptr || sms < 1 || B < 1 || V < 1 || K < 1 || split_k < 1) {
+        set_error("cb_decode_plan: bad arguments");
+        return CB_ERR_INVALID;
+    }
+    if (V > 0x7fffffff || K > 0x7fffffff || B > 0x7fffffff ||
+        !stream_plan_query(bits, (int)B, (int)V, (int)K, (int)std::min<int64_t>(split_k, 1 << 20), rho, sms, plan7)) {
+        set_error("cb_decode_plan: the ring kernel does not take this problem (bits 2/3/4, K %% 256 == 0, 1 <= B <= 8)");
+        return CB_ERR_UNSUPPORTED;
+    }
+    return CB_OK;
+}
+
 int cb_max_rho(int bits, int mode) {
     if (!(bits == 2 || bits == 3 || bits == 4)) { set_error("cb_max_rho: bits must be 2/3/4"); return -1; }
     if (mode < CB_MODE_GEMV || mode > CB_MODE_GATEUP) { set_error("cb_max_rho: unknown mode %d", mode); return -1; }
@@ -374,8 +389,15 @@ int cb_fused_qkv(const void* x, int64_t B, const cb_weight* q, const cb_weight* 
                       reinterpret_cast<cudaStream_t>(stream));
 }
 
-int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
-                   int64_t group_size, int dtype, int act, int use_tensor_cores, void* stream) {
+size_t cb_gemm_scratch_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const int sp = gemm_ws_splits(M, N, K);
+    return sp <= 1 ? 0 : (size_t)sp * (size_t)M * (size_t)N * sizeof(float);
+}
+
+int cb_packed_gemm_scratch(const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
+                           int64_t group_size, int dtype, int act, int use_tensor_cores, void* scratch,
+                           size_t scratch_bytes, void* stream) {
     int rc = check_common("packed_gemm", x, M, K, bits, group_size, dtype);
     if (rc) return rc;
     if ((rc = check_weight("packed_gemm", w, bits))) return rc;
@@ -384,11 +406,15 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out, int6
     CB_REQUIRE(out != nullptr, "packed_gemm: out is NULL");
     CB_REQUIRE(M < (1ll << 30), "packed_gemm: M out of range");
     if (use_tensor_cores && !g_force_generic) {
-        // tcgen05 kernels when the problem is inside their domain (-1 = it is not): above 128 tokens the one that
-        // keeps the expanded weights in tensor memory and serves 256 tokens per expansion, else the 128-token one
-        const bool ws_first = g_gemm_kernel == 2 || (g_gemm_kernel == 0 && (M > 128 || dtype == CB_BF16));
+        // tcgen05 kernels when the problem is inside their domain (-1 = it is not): above 128 tokens, for bf16, and
+        // wherever it can split K over otherwise idle SMs, the one that keeps the expanded weights in tensor memory
+        // and serves 256 tokens per expansion; else the 128-token one
+        const bool splits = scratch != nullptr && gemm_ws_splits(M, w->n, K) > 1 &&
+                            scratch_bytes >= (size_t)2 * M * w->n * sizeof(float);
+        const bool ws_first = g_gemm_kernel == 2 || (g_gemm_kernel == 0 && (M > 128 || dtype == CB_BF16 || splits));
         if (ws_first) {
-            const int rc3 = launch_gemm_ws(dtype, x, M, w, out, K, bits, group_size, act, reinterpret_cast<cudaStream_t>(stream));
+            const int rc3 = launch_gemm_ws(dtype, x, M, w, out, K, bits, group_size, act, reinterpret_cast<cudaStream_t>(stream),
+                                           scratch, scratch_bytes);
             if (rc3 != -1) return rc3;
         }
         const int rc2 = launch_gemm_tc(dtype, x, M, w, out, K, bits, group_size, act, reinterpret_cast<cudaStream_t>(stream));
@@ -397,6 +423,11 @@ int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out, int6
     const int round_w = (use_tensor_cores && dtype != CB_F32) ? 1 : 0;
     return launch_gemm_simt(dtype, x, M, w, out, K, bits, group_size, act, round_w,
                             reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cb_packed_gemm(const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
+                   int64_t group_size, int dtype, int act, int use_tensor_cores, void* stream) {
+    return cb_packed_gemm_scratch(x, M, w, out, K, bits, group_size, dtype, act, use_tensor_cores, nullptr, 0, stream);
 }
 
 int cb_fused_gate_up_gemm(const void* x, int64_t M, const cb_weight* gate, const cb_weight* up, void* out, int64_t K,

@@ -67,6 +67,10 @@ struct GemmParams {
     const __half* scales2; const __half* zeros2;     // fused gate/up: the up projection's metadata (scales / zeros are the gate's)
     int M, N, K, groups, group_size, act;
     int tiles_m, tiles_n, kblocks;
+    // K split (plain mode only): a work item is (tile, one of `splits` ranges of `kper` stages); with splits > 1 the
+    // items store fp32 partial sums [splits, M, N] and a second kernel adds them up
+    int splits, kper;
+    float* partial;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -327,8 +331,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    const int ntiles = P.tiles_m * P.tiles_n;
-    const int nsuper = (P.kblocks + 1) >> 1;                         // packed super-blocks per tile
+    const int nitems = P.tiles_m * P.tiles_n * P.splits;            // work item = (tile, K range): item / splits, item % splits
     int gave_up = 0;
 
     // Accumulator chunks (32 token columns each) cbegin, cbegin + cstep, ... of `tile` -> bias, activation, fp16, global.
@@ -336,7 +339,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     // one token's output row.
     // release_bar != 0: arrive on that barrier as soon as this warp's last chunk is in registers -- the accumulator may
     // then be overwritten; the conversion and the stores of that chunk follow the arrival.
-    auto drain = [&](int tile, int cbegin, int cstep, uint32_t release_bar) {
+    auto drain = [&](int item, int cbegin, int cstep, uint32_t release_bar) {
+        const int tile = item / P.splits, split = item - tile * P.splits;
         const int q = warp & 3;
         const int m0 = (tile % P.tiles_m) * kBT;
         const int row = q * 32 + lane;                              // TMEM lane
@@ -392,6 +396,17 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(release_bar);
+            }
+            if constexpr (MODE == 0) {
+                if (P.splits > 1) {      // partial sums of this K range: fp32, [split][token][weight row]
+                    if (nlive) {
+                        float* pcol = P.partial + ((size_t)split * P.M + m0 + c0) * P.N + n;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (m0 + c0 + j < P.M) pcol[(size_t)j * P.N] = __uint_as_float(v[j]);
+                    }
+                    continue;
+                }
             }
             if constexpr (GU) {
                 // silu(gate) * up: the gate lane and the up lane of an output column share the work -- the gate lane
@@ -484,9 +499,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // ================= TMA producer: activation tiles, 256 tokens x 64 codes =================
         if (lane == 0) {
             int it = 0;
-            for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x) {
+            for (int item = blockIdx.x; item < nitems && !gave_up; item += gridDim.x) {
+                const int tile = item / P.splits, kb0 = (item - tile * P.splits) * P.kper;
                 const int m0 = (tile % P.tiles_m) * kBT;
-                for (int kb = 0; kb < P.kblocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb0 + P.kper; ++kb, ++it) {
                     const int s = it % kStages;
                     if (it >= kStages && !mbar_wait(empty(s), ((it / kStages) - 1) & 1, abort_flag)) { gave_up = 1; break; }
                     mbar_expect_tx(full_x(s), kXBytes);
@@ -498,7 +514,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // ================= TMA producer: packed words, 128 rows x 128 codes per box =================
         if (lane == 0) {
             int pit = 0;
-            for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x) {
+            for (int item = blockIdx.x; item < nitems && !gave_up; item += gridDim.x) {
+                const int tile = item / P.splits, kb0 = (item - tile * P.splits) * P.kper;
                 int n0 = (tile / P.tiles_m) * kOutCols;
                 const CUtensorMap* map = &wmap;
                 if constexpr (QKV) {      // the tile's projection has its own packed tensor
@@ -506,7 +523,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     tile_proj(tile / P.tiles_m, proj, n0);
                     map = proj == 0 ? &wmap : proj == 1 ? &wmap2 : &wmap3;
                 }
-                for (int sb = 0; sb < nsuper; ++sb, ++pit) {
+                for (int sb = kb0 >> 1; sb < ((kb0 + P.kper) >> 1); ++sb, ++pit) {      // kper is even
                     const int slot = pit % kPackedSlots;
                     if (pit >= kPackedSlots && !mbar_wait(empty_p(slot), ((pit / kPackedSlots) - 1) & 1, abort_flag)) { gave_up = 5; break; }
                     mbar_expect_tx(full_p(slot), kBN * kRowBytes);
@@ -521,11 +538,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // ================= MMA issuer: A (weights) from tensor memory, B (activations) from shared memory =================
         if (lane == 0) {
             int it = 0, tcount = 0;
-            for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x, ++tcount) {
-                // the one accumulator must have been drained by the epilogue of the previous tile
+            for (int item = blockIdx.x; item < nitems && !gave_up; item += gridDim.x, ++tcount) {
+                // the one accumulator must have been drained by the epilogue of the previous item
                 if (tcount >= 1 && !mbar_wait(tmem_empty, (tcount - 1) & 1, abort_flag)) { gave_up = 2; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int kb = 0; kb < P.kblocks; ++kb, ++it) {
+                for (int kb = 0; kb < P.kper; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
                     if (!mbar_wait(full_x(s), ph, abort_flag) || !mbar_wait(full_w(s), ph, abort_flag)) { gave_up = 2; break; }
@@ -547,7 +564,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 }
                 if (gave_up) break;
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tmem_full) : "memory");
-                if (tile + (int)gridDim.x >= ntiles)     // also wakes the dequantiser warps, which help drain the last tile
+                if (item + (int)gridDim.x >= nitems)     // also wakes the dequantiser warps, which help drain the last item
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(final_full) : "memory");
             }
         }
@@ -560,18 +577,20 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         const int q = warp & 3;                                           // the TMEM lane quadrant this warp may access
         const int grp = (warp - kFirstDequantWarp) >> 2;                  // 0..3
         const int r = q * 32 + lane;                                      // weight row of the tile = TMEM lane
-        const int my_tiles = blockIdx.x < ntiles ? (ntiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-        const int total = my_tiles * P.kblocks;                           // stages this CTA runs through
+        const int my_tiles = blockIdx.x < nitems ? (nitems - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;   // work items of this CTA
+        const int total = my_tiles * P.kper;                              // stages this CTA runs through
         const unsigned short* srow = nullptr;
         const unsigned short* zrow = nullptr;
         int cur_tile_local = -1;
         bool live = false;
         auto meta_of = [&](int it) -> uint32_t {                          // (zero << 16) | scale of (row, stage it), raw fp16 bits
             if (it >= total) return 0u;
-            const int tl = it / P.kblocks, kb = it - tl * P.kblocks;
+            const int tl = it / P.kper;
+            const int item = blockIdx.x + tl * gridDim.x;
+            const int tile = item / P.splits;
+            const int kb = (item - tile * P.splits) * P.kper + (it - tl * P.kper);
             if (tl != cur_tile_local) {
                 cur_tile_local = tl;
-                const int tile = blockIdx.x + tl * gridDim.x;
                 int n = (tile / P.tiles_m) * kOutCols + (GU ? (r >> 1) : r);
                 live = n < P.N;
                 int proj = (GU && (r & 1)) ? 1 : 0;                      // odd lanes of a fused gate/up tile belong to the up projection
@@ -675,10 +694,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     } else if (warp < kPackedWarp) {
         // ================= epilogue warps: drain every accumulator; on the CTA's last tile the dequantisers help =================
         int tcount = 0;
-        for (int tile = blockIdx.x; tile < ntiles && !gave_up; tile += gridDim.x, ++tcount) {
+        for (int tile = blockIdx.x; tile < nitems && !gave_up; tile += gridDim.x, ++tcount) {      // `tile` counts work items here
             if (!__all_sync(0xffffffffu, mbar_wait(tmem_full, tcount & 1, abort_flag))) { gave_up = 4; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const bool last = tile + (int)gridDim.x >= ntiles;
+            const bool last = tile + (int)gridDim.x >= nitems;
             const int worker = (warp - kFirstEpiWarp) >> 2;             // this warp's place among its quadrant's epilogue warps
             // Plain and gate/up: the arrival that frees the accumulator comes before the last chunk's stores (measured
             // 3-4 % faster); with the Q/K/V epilogue the same order was measured 15 % slower, so there it follows the drain.
@@ -722,6 +741,37 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// out[m, n] = act(sum over the K ranges of partial[s, m, n] + bias[n]) for a K-split launch: four columns per thread.
+template <bool BF>
+__global__ void gemm_ws_reduce_kernel(const float* __restrict__ partial, const __half* __restrict__ bias, __half* __restrict__ out,
+                                      int M, int N, int splits, int act) {
+    const size_t quads = (size_t)M * N / 4;
+    for (size_t q = blockIdx.x * (size_t)blockDim.x + threadIdx.x; q < quads; q += (size_t)gridDim.x * blockDim.x) {
+        float4 acc = reinterpret_cast<const float4*>(partial)[q];
+        for (int s = 1; s < splits; ++s) {
+            const float4 v = reinterpret_cast<const float4*>(partial + (size_t)s * M * N)[q];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int n = (int)((q * 4) % N);
+        float y[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (bias != nullptr)
+                y[i] += BF ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[n + i]) : __half2float(bias[n + i]);
+            y[i] = activate(y[i], act);
+        }
+        if constexpr (BF) {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + q * 4;
+            reinterpret_cast<__nv_bfloat162*>(o)[0] = __floats2bfloat162_rn(y[0], y[1]);
+            reinterpret_cast<__nv_bfloat162*>(o)[1] = __floats2bfloat162_rn(y[2], y[3]);
+        } else {
+            __half* o = out + q * 4;
+            reinterpret_cast<__half2*>(o)[0] = __floats2half2_rn(y[0], y[1]);
+            reinterpret_cast<__half2*>(o)[1] = __floats2half2_rn(y[2], y[3]);
+        }
+    }
+}
+
 template <int BITS, bool BF, int MODE>
 int launch_t(const CUtensorMap& xmap, const CUtensorMap& wmap, const CUtensorMap& wmap2, const CUtensorMap& wmap3,
              const GemmParams& P, const QkvParams& Q, int grid, cudaStream_t stream) {
@@ -750,8 +800,21 @@ struct WsQkv {
     int head_dim, perm_hd;
 };
 
+// How many K ranges a plain launch of this shape is split into when `scratch_bytes` of scratch are available: only where
+// the tiles alone would leave more than half of the SMs idle, at least eight stages per range, ranges of equal size.
+int ws_splits(int64_t M, int64_t N, int64_t K, int sms, size_t scratch_bytes) {
+    const int64_t tiles = ((M + kBT - 1) / kBT) * ((N + kBN - 1) / kBN);
+    const int supers = (int)(K / (2 * kBK));
+    if (tiles * 2 > sms || N % 4 != 0 || K % 128 != 0) return 1;
+    int best = 1;
+    for (int sp = 2; sp <= 8 && tiles * sp <= sms && supers / sp >= 4; ++sp)
+        if (supers % sp == 0 && (size_t)sp * M * N * sizeof(float) <= scratch_bytes) best = sp;
+    return best;
+}
+
 int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_weight* w2, void* out, int64_t K, int bits,
-              int64_t gs, int act, cudaStream_t stream, const WsQkv* qkv = nullptr) {
+              int64_t gs, int act, cudaStream_t stream, const WsQkv* qkv = nullptr, void* scratch = nullptr,
+              size_t scratch_bytes = 0) {
     const bool gu = w2 != nullptr && qkv == nullptr;
     if ((dtype != CB_F16 && dtype != CB_BF16) || K % 128 != 0 || gs % kBK != 0 || M < 1) return -1;
     if (!gu && w->n % 8 != 0) return -1;
@@ -832,19 +895,32 @@ int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_
         Q.head_dim = qkv->head_dim; Q.perm_hd = qkv->perm_hd;
         P.act = 0;
     }
-    const int grid = std::min(sms, P.tiles_m * P.tiles_n);
     const bool bf = dtype == CB_BF16;
     const int mode = qkv != nullptr ? 2 : gu ? 1 : 0;
+    P.splits = 1;
+    if (mode == 0 && scratch != nullptr && reinterpret_cast<uintptr_t>(scratch) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0)
+        P.splits = ws_splits(M, w->n, K, sms, scratch_bytes);
+    P.kper = P.kblocks / P.splits;
+    P.partial = P.splits > 1 ? reinterpret_cast<float*>(scratch) : nullptr;
+    const int grid = std::min(sms, P.tiles_m * P.tiles_n * P.splits);
+    int rc_launch;
 #define CB_WS_LAUNCH_M(B, MD) \
     (bf ? launch_t<B, true, MD>(xmap, wmap, wmap2, wmap3, P, Q, grid, stream) : launch_t<B, false, MD>(xmap, wmap, wmap2, wmap3, P, Q, grid, stream))
 #define CB_WS_LAUNCH(B) (mode == 2 ? CB_WS_LAUNCH_M(B, 2) : mode == 1 ? CB_WS_LAUNCH_M(B, 1) : CB_WS_LAUNCH_M(B, 0))
     switch (bits) {
-        case 2: return CB_WS_LAUNCH(2);
-        case 3: return CB_WS_LAUNCH(3);
-        default: return CB_WS_LAUNCH(4);
+        case 2: rc_launch = CB_WS_LAUNCH(2); break;
+        case 3: rc_launch = CB_WS_LAUNCH(3); break;
+        default: rc_launch = CB_WS_LAUNCH(4); break;
     }
 #undef CB_WS_LAUNCH
 #undef CB_WS_LAUNCH_M
+    if (rc_launch != CB_OK || P.splits == 1) return rc_launch;
+    const int rthreads = 256;
+    const int rgrid = (int)std::min<size_t>(((size_t)M * w->n / 4 + rthreads - 1) / rthreads, (size_t)sms * 8);
+    if (bf) gemm_ws_reduce_kernel<true><<<rgrid, rthreads, 0, stream>>>(P.partial, P.bias, P.out, P.M, P.N, P.splits, P.act);
+    else gemm_ws_reduce_kernel<false><<<rgrid, rthreads, 0, stream>>>(P.partial, P.bias, P.out, P.M, P.N, P.splits, P.act);
+    CB_CUDA_TRY(cudaGetLastError());
+    return CB_OK;
 }
 
 }  // namespace
@@ -853,8 +929,14 @@ int launch_ws(int dtype, const void* x, int64_t M, const cb_weight* w, const cb_
 // domain (fp16 or bf16, K a multiple of 128, group size a multiple of 64, N a multiple of 8, 16-byte aligned
 // x / packed) and the caller should use another kernel.
 int launch_gemm_ws(int dtype, const void* x, int64_t M, const cb_weight* w, void* out, int64_t K, int bits,
-                   int64_t gs, int act, cudaStream_t stream) {
-    return launch_ws(dtype, x, M, w, nullptr, out, K, bits, gs, act, stream);
+                   int64_t gs, int act, cudaStream_t stream, void* scratch, size_t scratch_bytes) {
+    return launch_ws(dtype, x, M, w, nullptr, out, K, bits, gs, act, stream, nullptr, scratch, scratch_bytes);
+}
+
+// Splits a plain launch of this shape would use with unlimited scratch (1 = no split), for sizing that scratch.
+int gemm_ws_splits(int64_t M, int64_t N, int64_t K) {
+    const int sms = sm_count_current();
+    return sms <= 0 ? 1 : ws_splits(M, N, K, sms, ~(size_t)0);
 }
 
 // Fused prefill gate/up: out[M, n] = silu(x Wg^T) * (x Wu^T) in one launch; same return convention.

@@ -54,7 +54,7 @@ constexpr int kThreads = 32 * kWarps;
 constexpr int kRowLanes = kThreads / 32;        // threads that share one row of a pass when copies are issued and results reduced
 constexpr int kMaxBuf = 6;
 constexpr int kSpinLimit = 1 << 22;           // bounded mbarrier wait (~ a second), then give up and flag
-constexpr size_t kSmemCap = 220 * 1024;       // one CTA per SM
+constexpr size_t kSmemCap = 226 * 1024;       // one CTA per SM
 constexpr size_t kSmemCapTwo = 112 * 1024;    // two CTAs per SM
 
 __device__ int g_stream_status;               // 0 = ok; k > 0: the copy of pass k-1 never landed
@@ -68,7 +68,7 @@ struct StreamParams {
     GemvParams g;
     int nslabs;            // CTAs per K-partition
     int nbuf;              // ring depth
-    int rpp;               // rows per pass: 32 or 16
+    int rpp;               // rows per pass: 16 to 32, even
     int pitch;             // shared-memory bytes per staged row (row bytes + bank-spreading pad)
     int meta_stride;       // shared-memory bytes per staged row of scales (and of zeros)
     int slot_bytes;        // one ring slot: rpp weight rows, rpp scale rows, rpp zero rows
@@ -197,8 +197,7 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
     // one warp are issued one after the other); every thread copies its share of the row's scales and zeros, 4 bytes
     // (two groups) per cp.async.  The slot's mbarrier completes after the expect-tx arrival, the bulk bytes, and one
     // arrival per thread once its cp.async have landed.
-    auto issue_pass = [&](int p) {
-        const int buf = p % S.nbuf;
+    auto issue_pass = [&](int p, int buf) {
         const int row0 = row_begin + p * rpp;
         const int nrows = min(rpp, row_end - row0);
         const uint32_t slot = s_ring + (uint32_t)buf * S.slot_bytes;
@@ -224,7 +223,7 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
         }
         cp_async_arrive_noinc(bar);
     };
-    for (int p = 0; p < min(npass, S.nbuf); ++p) issue_pass(p);
+    for (int p = 0; p < min(npass, S.nbuf); ++p) issue_pass(p, p);
     // Touch the activations' pages now (the values may be stale and are not used): address translation and the
     // request path are then warm when the real loads follow the hand-over.
     if (lane == 0) {
@@ -256,7 +255,8 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
             const int id = first + lane;
             const bool on = id < ntask;
             const int q = id >> 2, tq = id & 3;
-            const int gl = wg_begin + q / P.B, b = q % P.B;
+            const int ql = P.B == 1 ? q : q / P.B;
+            const int gl = wg_begin + ql, b = q - ql * P.B;
             uint32_t raw[16];
             if (on) {
                 const uint4* xp = reinterpret_cast<const uint4*>(x + 2 * ((size_t)b * P.K + (size_t)(g_begin + gl) * 128 + tq * 32));
@@ -317,7 +317,8 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
                 for (int j = 0; j < 2; ++j) {
                     const int qq = q0 + j;
                     if (4 * qq < ntask) {
-                        const int at = (wg_begin + qq / P.B) * 8 + qq % P.B;
+                        const int gq = P.B == 1 ? qq : qq / P.B;
+                        const int at = (wg_begin + gq) * 8 + (qq - gq * P.B);
                         xsum[at] = (j ? x1 : x0) * (1.0f / F::kInvUnit);
                         if constexpr (F::kBase != 0.f) xsum[S.g.groups * 8 + at] = j ? c1 : c0;
                     }
@@ -333,10 +334,10 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
     const uint32_t x_step = has_x ? (uint32_t)(P.B * 4 * kXBlock) : 0u;
     const uint32_t p8 = 8u * S.pitch, m8 = 8u * S.meta_stride;
     const int ngw = wg_end - wg_begin;
+    int buf = 0;
+    uint32_t parity = 0u;              // ring slot of pass p and the phase of its mbarrier: p % nbuf, (p / nbuf) & 1
     for (int p = 0; p < npass; ++p) {
-        const int buf = p % S.nbuf;
         const int row0 = row_begin + p * rpp;
-        const uint32_t parity = (uint32_t)((p / S.nbuf) & 1);
         const int ntile = (min(rpp, row_end - row0) + 15) >> 4;
         const uint32_t slot = s_ring + (uint32_t)buf * S.slot_bytes;
         float* myred = red + (size_t)(p & 1) * red_floats;
@@ -487,7 +488,7 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
         // the ring slot is free again: refill it with pass p + nbuf
         if (p + S.nbuf < npass) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            issue_pass(p + S.nbuf);
+            issue_pass(p + S.nbuf, buf);
         }
         {
             // thread -> (row of the pass, batch column, share of the warps); the shares meet through shuffles
@@ -531,6 +532,7 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
                 else P.partial[((size_t)split * P.B + b) * P.V + v] = mine;
             }
         }
+        if (++buf == S.nbuf) { buf = 0; parity ^= 1u; }
     }
     if (failed) atomicExch(&g_stream_status, failed);
 
@@ -627,71 +629,88 @@ bool conflicts(const LaunchRec& a, const LaunchRec& b) {
     return false;
 }
 
-template <int BITS, int KIND>
-int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, void* scratch, size_t scratch_bytes,
-             cudaStream_t stream) {
-    const int sms = sm_count_current();
-    if (sms <= 0) return CB_ERR_CUDA;
-    StreamParams S{};
+// Shared-memory layout of one CTA for K split `sp`, ring depth `nbuf` and `rpp` rows per pass; returns its size.
+// *overrun is set when a tile of the last ring slot would be read past the end of the allocation.
+size_t stream_layout(int bits, int B, int groups, int sp, int nbuf, int rpp, StreamParams& out, bool* overrun) {
+    const int gpairs = groups / 2;
+    const int group_bytes = 16 * bits;
+    const int ng = 2 * ((gpairs + sp - 1) / sp);                  // largest partition
+    int meta = ng * 2;
+    meta += ((4 - meta) % 128 + 128) % 128;                        // rows 4 bytes apart (mod 128): conflict-free 2-byte reads
+    int pitch = ng * group_bytes;
+    pitch += ((group_bytes - pitch) % 128 + 128) % 128;           // pitch == group_bytes (mod 128): conflict-free fragment reads
+    size_t off = 0;
+    out.off_bar = (unsigned)off; off += 128;                     // one mbarrier per ring slot (at most 8), then 64 zero bytes
+    // The ring comes first.  A pass shorter than its tiles (16 rows each) still reads, and discards, the ring bytes of
+    // the absent rows: past the last slot those reads land in the regions below, inside the allocation.
+    out.slot_bytes = rpp * (pitch + 2 * meta);
+    out.off_ring = (unsigned)off; off += (size_t)nbuf * out.slot_bytes;
+    off = (off + 127) & ~(size_t)127;
+    out.off_red = (unsigned)off; off += (size_t)2 * (kWarps * 2 * 8 * ((B + 1) / 2) * 4 + kWarps * 32 * B) * sizeof(float);
+    out.off_xsum = (unsigned)off; off += (size_t)2 * groups * 8 * sizeof(float);
+    off = (off + 127) & ~(size_t)127;
+    out.off_xs = (unsigned)off; off += (size_t)ng * B * 4 * kXBlock;   // staged activations of one partition
+    out.pitch = pitch; out.meta_stride = meta; out.nbuf = nbuf; out.rpp = rpp;
+    const size_t tile_rows = (size_t)((rpp + 15) / 16) * 16;
+    const size_t reach = (size_t)out.off_ring + (size_t)(nbuf - 1) * out.slot_bytes + tile_rows * pitch;
+    if (overrun) *overrun = reach > off;
+    return off;
+}
+
+// The launch plan of the ring kernel: K split, row slabs, rows per pass, ring depth.  Pure host arithmetic.
+struct StreamPlan { int split, rpp, nbuf, nslabs, npass; size_t smem; bool ok; };
+
+bool plan_stream(int bits, int B, int V, int groups, int split_k, int64_t rho, int sms, StreamPlan* out) {
     // K-partitions are whole PAIRS of groups (4-byte granularity of the metadata copies); the caller's
     // split_k is raised if the activations of one partition would not fit beside the weight ring.
-    const int gpairs = P.groups / 2;
-    int split = std::max(1, std::min(P.split_k, gpairs));
-    const int group_bytes = 16 * BITS;
-    auto layout = [&](int sp, int nbuf, int rpp, StreamParams& out) -> size_t {
-        const int ng = 2 * ((gpairs + sp - 1) / sp);                  // largest partition
-        int meta = ng * 2;
-        meta += ((4 - meta) % 128 + 128) % 128;                        // rows 4 bytes apart (mod 128): conflict-free 2-byte reads
-        int pitch = ng * group_bytes;
-        pitch += ((group_bytes - pitch) % 128 + 128) % 128;           // pitch == group_bytes (mod 128): conflict-free fragment reads
-        size_t off = 0;
-        out.off_bar = (unsigned)off; off += 128;                     // one mbarrier per ring slot (at most 8), then 64 zero bytes
-        off = (off + 127) & ~(size_t)127;
-        out.off_red = (unsigned)off; off += (size_t)2 * (kWarps * 2 * 8 * ((P.B + 1) / 2) * 4 + kWarps * 32 * P.B) * sizeof(float);
-        out.off_xsum = (unsigned)off; off += (size_t)2 * P.groups * 8 * sizeof(float);
-        off = (off + 127) & ~(size_t)127;
-        out.off_xs = (unsigned)off; off += (size_t)ng * P.B * 4 * kXBlock;   // staged activations of one partition
-        off = (off + 127) & ~(size_t)127;
-        out.slot_bytes = rpp * (pitch + 2 * meta);
-        out.off_ring = (unsigned)off; off += (size_t)nbuf * out.slot_bytes;
-        out.pitch = pitch; out.meta_stride = meta; out.nbuf = nbuf; out.rpp = rpp;
-        return off;
-    };
+    const int gpairs = groups / 2;
+    if (gpairs < 1 || V < 1 || sms < 1) return false;
+    const int split = std::max(1, std::min(split_k, gpairs));
     // slabs are whole row PAIRS (the two operands of silu(gate)*up and of a rotation are neighbouring rows)
     const int gran = 2;
-    const int vpairs = (P.V + gran - 1) / gran;
+    const int vpairs = (V + gran - 1) / gran;
     // Slabs, passes and ring depth of a candidate (CTAs, split, rows per pass) under a shared-memory cap.
-    struct Plan { int split, rpp, nbuf, nslabs, npass; bool ok; };
-    auto plan = [&](int ctas, int sp, int rpp, size_t cap) -> Plan {
-        Plan pl{sp, rpp, 0, 0, 0, false};
+    auto plan = [&](int ctas, int sp, int rpp, size_t cap) -> StreamPlan {
+        StreamPlan pl{sp, rpp, 0, 0, 0, 0, false};
         StreamParams tmp{};
-        if (layout(sp, 1, rpp, tmp) > cap) return pl;
+        bool overrun = false;
         int nslabs = std::max(1, std::min(ctas / sp, (gran * vpairs + 15) / 16));          // at least 16 rows per slab when possible
         nslabs = std::min(nslabs, vpairs);
         const int rows_per_slab = gran * ((vpairs + nslabs - 1) / nslabs);
+        // a slab shorter than a pass: the slot holds only the slab's rows (never fewer than 16: the scale reads of a
+        // tile's absent rows then stay inside the slot's metadata)
+        pl.rpp = std::max(16, std::min(rpp, rows_per_slab));
+        if (stream_layout(bits, B, groups, sp, 1, pl.rpp, tmp, &overrun) > cap || overrun) return pl;
         pl.nslabs = nslabs;
-        pl.npass = (rows_per_slab + rpp - 1) / rpp;
+        pl.npass = (rows_per_slab + pl.rpp - 1) / pl.rpp;
         pl.nbuf = std::min(pl.npass, kMaxBuf);
-        while (pl.nbuf > 1 && layout(sp, pl.nbuf, rpp, tmp) > cap) --pl.nbuf;
-        pl.ok = true;
+        while (pl.nbuf > 1 && (stream_layout(bits, B, groups, sp, pl.nbuf, pl.rpp, tmp, &overrun) > cap || overrun)) --pl.nbuf;
+        pl.smem = stream_layout(bits, B, groups, sp, pl.nbuf, pl.rpp, tmp, &overrun);
+        pl.ok = !overrun;
         return pl;
     };
-    // (1) One CTA per SM covers its rows in a single 32-row pass: do that, and leave the SM's second CTA slot to
-    //     the next launch of the stream, whose prologue and first copies then overlap this launch's arithmetic.
-    // (2) Otherwise prefer a ring that keeps copies in flight during the arithmetic (two slots or more): two CTAs
-    //     per SM (twice the warps to hide latency) with 32- or 16-row passes, else one CTA per SM likewise.
+    // rho is the number of CTAs per SM the row slabs are cut for (0: chosen here).
+    // (1) If one CTA per SM covers its rows in a single pass of at most 32 rows inside half an SM's shared memory, do
+    //     that and leave the SM's second CTA slot to the next launch of the stream, whose prologue and first copies
+    //     then overlap this launch's arithmetic.
+    // (2) Otherwise a ring that keeps copies in flight during the arithmetic (two slots or more, or the whole slab in
+    //     one pass), tried in the order the caller's rho asks for: one CTA per SM with all of its shared memory
+    //     (32-row passes: two 16-row tiles per step, eight accumulation chains per warp), or two CTAs per SM with
+    //     half each (32- or 16-row passes).
     // (3) Otherwise one CTA per SM with a single slot, the K split raised until a slot fits.
-    const int per_sm = rho <= 0 ? 2 : (int)std::min<int64_t>(std::max<int64_t>(rho, 2), 4);
-    Plan pick{};
+    StreamPlan pick{};
     {
-        const Plan c = plan(sms, split, 32, kSmemCapTwo);
-        if (rho > 0 && rho <= 2 && c.ok && c.npass == 1) pick = c;
+        const StreamPlan c = plan(sms, split, 32, kSmemCapTwo);
+        if (rho <= 2 && c.ok && c.npass == 1) pick = c;
     }
     if (!pick.ok) {
-        const struct { int ctas; size_t cap; } tries[2] = {{per_sm * sms, kSmemCapTwo}, {sms, kSmemCap}};
+        const bool one_first = rho <= 1;
+        struct Try { int ctas; size_t cap; };
+        const Try one{sms, kSmemCap}, two{2 * sms, kSmemCapTwo};
+        const Try tries[2] = {one_first ? one : two, one_first ? two : one};
         for (int i = 0; i < 2 && !pick.ok; ++i)
             for (int rpp : {32, 16}) {
-                const Plan c = plan(tries[i].ctas, split, rpp, tries[i].cap);
+                const StreamPlan c = plan(tries[i].ctas, split, rpp, tries[i].cap);
                 if (c.ok && c.nbuf >= std::min(2, c.npass)) { pick = c; break; }
             }
     }
@@ -699,9 +718,24 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
         int sp = split;
         while (!plan(sms, sp, 32, kSmemCap).ok && sp < gpairs) ++sp;
         pick = plan(sms, sp, 32, kSmemCap);
-        if (!pick.ok) return -1;
+        if (!pick.ok) return false;
     }
-    split = pick.split;
+    *out = pick;
+    return true;
+}
+
+template <int BITS, int KIND>
+int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, void* scratch, size_t scratch_bytes,
+             cudaStream_t stream) {
+    const int sms = sm_count_current();
+    if (sms <= 0) return CB_ERR_CUDA;
+    StreamParams S{};
+    StreamPlan pick{};
+    if (!plan_stream(BITS, P.B, P.V, P.groups, P.split_k, rho, sms, &pick)) return -1;
+    const int gran = 2;
+    const int vpairs = (P.V + gran - 1) / gran;
+    const int gpairs = P.groups / 2;
+    int split = pick.split;
     const int nslabs = pick.nslabs;
     if (split > 1 && nslabs > 65536) return -1;
     // scratch: [65536 counters | split x B x V partial sums]; without enough of it this path is not taken
@@ -712,7 +746,7 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
         P.counters = reinterpret_cast<int*>(scratch);
         P.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kCounterBytes);
     }
-    const size_t smem = layout(split, pick.nbuf, pick.rpp, S);
+    const size_t smem = stream_layout(BITS, P.B, P.groups, split, pick.nbuf, pick.rpp, S, nullptr);
     P.split_k = split;
     S.g = P;
     S.nslabs = nslabs;
@@ -811,6 +845,18 @@ int launch_gemv_stream(int bits, int dtype, const void* x, const GemvParams& P, 
     CB_STREAM_CASE(2, kFragMagicB) CB_STREAM_CASE(3, kFragMagicB) CB_STREAM_CASE(4, kFragMagicB)
 #undef CB_STREAM_CASE
     return -1;
+}
+
+// out7 = {grid, dynamic shared memory bytes, K split, rows per pass, ring slots, passes per CTA, row slabs}; false when the
+// ring kernel does not take this problem.
+bool stream_plan_query(int bits, int B, int V, int K, int split_k, int64_t rho, int sms, long long* out7) {
+    if (K % 256 != 0 || B < 1 || B > kMaxBatchBlock || (bits != 2 && bits != 3 && bits != 4)) return false;
+    StreamPlan pl{};
+    if (!plan_stream(bits, B, V, K / 128, split_k, rho, sms, &pl)) return false;
+    if (pl.split > 1 && pl.nslabs > 65536) return false;
+    out7[0] = (long long)pl.nslabs * pl.split; out7[1] = (long long)pl.smem; out7[2] = pl.split; out7[3] = pl.rpp;
+    out7[4] = pl.nbuf; out7[5] = pl.npass; out7[6] = pl.nslabs;
+    return true;
 }
 
 void chain_stats(long long* out4) {

@@ -41,3 +41,35 @@ def test_product_package_does_not_reach_into_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "cb_oracle" not in src and "import oracle" not in src and "from oracle" not in src, f
+
+
+def test_decode_plan_is_host_arithmetic_and_stays_inside_an_sm():
+    """cb_decode_plan needs no GPU.  Every plan covers all rows, fits the 227 KB a CTA may ask for, and a plan meant to
+    share an SM between two CTAs fits half of it."""
+    lib = ctypes.CDLL(os.path.join(PKG, "lib", "libcrispybits_b200.so"))
+    lib.cb_decode_plan.argtypes = [ctypes.c_int] + [ctypes.c_int64] * 5 + [ctypes.c_int, ctypes.POINTER(ctypes.c_longlong)]
+    out = (ctypes.c_longlong * 7)()
+    shapes = [(4096, 4096), (11008, 4096), (4096, 11008), (22016, 4096), (12288, 4096), (512, 4096), (32000, 4096),
+              (64, 256), (2, 256), (130, 512), (4096, 14336), (28672, 8192)]
+    seen_two_per_sm = False
+    for n, k in shapes:
+        for bits in (2, 3, 4):
+            for batch in (1, 2, 5, 8):
+                for split_k in (1, 2, 4):
+                    for rho in (0, 1, 2, 4):
+                        for sms in (148, 132, 8):
+                            rc = lib.cb_decode_plan(bits, batch, n, k, split_k, rho, sms, out)
+                            assert rc == 0, (n, k, bits, batch, split_k, rho, sms)
+                            grid, smem, split, rpp, slots, passes, slabs = (int(v) for v in out)
+                            assert grid == slabs * split and grid >= 1
+                            assert split >= min(split_k, k // 256) and 16 <= rpp <= 32 and rpp % 2 == 0
+                            assert 1 <= slots <= passes
+                            assert slabs * passes * rpp >= n, "the passes of all slabs cover every row"
+                            assert smem <= 227 * 1024
+                            if grid > sms and split == 1:
+                                assert smem <= 112 * 1024
+                                seen_two_per_sm = True
+    assert seen_two_per_sm
+    # outside the kernel's domain: K not a multiple of 256, batch above 8
+    assert lib.cb_decode_plan(4, 1, 4096, 4096 + 128, 1, 1, 148, out) != 0
+    assert lib.cb_decode_plan(4, 9, 4096, 4096, 1, 1, 148, out) != 0
