@@ -253,12 +253,14 @@ void cb_set_option(int option, int value);
 int cb_chain_stats(long long* counts4);
 
 /* The launch plan the ring decode kernel would use for a GEMV with batch B (1..8), V virtual output rows, reduction
- * length K (a multiple of 256, group size 128), the caller's split_k and rho, on a GPU with `sms` multiprocessors.
- * Pure host arithmetic: needs no GPU and launches nothing.  plan7 receives {grid, dynamic shared memory bytes,
- * K split used, rows per pass, ring slots, passes per CTA, row slabs}.  rho = 1 asks for one CTA per SM with all of
- * its shared memory, rho = 2 for two CTAs per SM with half each; either falls back to the other when its ring does
- * not fit.  CB_ERR_UNSUPPORTED when the kernel does not take the problem (the call then runs the generic kernel).
- * Stands where packed_gemv.cu:184-188 and host_utils.h:90-93 (cb_blocks) compute the grid from rho and the SM count. */
+ * length K (a multiple of 256, group size 128) and the caller's split_k, on a GPU with `sms` multiprocessors.  Pure
+ * host arithmetic: needs no GPU and launches nothing.  plan7 receives {grid, dynamic shared memory bytes, K split
+ * used, rows per pass, ring slots, passes per CTA, row slabs}.
+ * rho: where packed_gemv.cu:184-188 and host_utils.h:90-93 (cb_blocks) size a persistent grid of rho * SMs blocks, the
+ * ring kernel sizes its own grid from what fits an SM's shared memory (two CTAs per SM with half of it each where the
+ * ring fits, else one), so rho >= 0 does not change its plan; rho < 0 makes it try one CTA per SM first (a tuning and
+ * test knob).  The shape-generic kernel honours rho as the reference does.
+ * CB_ERR_UNSUPPORTED when the ring kernel does not take the problem (the call then runs the generic kernel). */
 int cb_decode_plan(int bits, int64_t B, int64_t V, int64_t K, int64_t split_k, int64_t rho, int sms, long long* plan7);
 
 /* Synchronises the device, then returns in *status the decode kernels' error word and clears it:

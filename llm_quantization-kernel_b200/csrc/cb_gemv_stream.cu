@@ -490,44 +490,27 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue_pass(p + S.nbuf, buf);
         }
-        {
-            // thread -> (row of the pass, batch column, share of the warps); the shares meet through shuffles
-            constexpr int kShares = kRowLanes / 8;
-            const int r32 = tid / kRowLanes, b = (tid % kRowLanes) / kShares, h = tid % kShares;
-            const int tile = r32 >> 4, r = r32 & 15;
-            const int v = row0 + r32;
-            const int bb = b < P.B ? b : 0;
+        // ---- reduction over the warps and final step: warp -> batch row (rotating with the pass, so that the warps
+        //      without one are already in the next pass), lane -> row of the pass
+        const int b = (warp + kWarps - (p & (kWarps - 1))) & (kWarps - 1);
+        if (b < P.B) {
+            const int tile = lane >> 4, r = lane & 15;
+            const int v = row0 + lane;
             // element of the partial-sum block of a (warp, tile): row pair r & 7, lane t = b / 2, value (r / 8) * 2 + (b & 1)
-            const int fe = (r >> 3) * 2 + (bb & 1);
-            const int fl = ((r & 7) * tcols + (bb >> 1)) * 4 + fe;
-            const int pl = (((r ^ 1) & 7) * tcols + (bb >> 1)) * 4 + fe;
             const int wstride = 2 * 8 * tcols * 4;
-            const float* ared = myred + tile * 8 * tcols * 4 + h * (kWarps / kShares) * wstride;
-            const float* cred = myred + acc_floats + (h * (kWarps / kShares) * 32 + r32) * P.B + bb;
-            float mine = 0.f, partner = 0.f, cm = 0.f, cp = 0.f;
+            const float* ared = myred + ((tile * 8 + (r & 7)) * tcols + (b >> 1)) * 4 + (r >> 3) * 2 + (b & 1);
+            const float* cred = myred + acc_floats + lane * P.B + b;
+            float mine = 0.f, cm = 0.f;
 #pragma unroll
-            for (int w = 0; w < kWarps / kShares; ++w) {
-                mine += ared[w * wstride + fl];
+            for (int w = 0; w < kWarps; ++w) {
+                mine += ared[w * wstride];
                 cm += cred[w * 32 * P.B];
             }
-            mine -= cm;
-#pragma unroll
-            for (int o = 1; o < kShares; o <<= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
-            mine *= F::kInvUnit;
-            if (P.mode != CB_MODE_GEMV) {
-                const float* pred = myred + acc_floats + (h * (kWarps / kShares) * 32 + (r32 ^ 1)) * P.B + bb;
-#pragma unroll
-                for (int w = 0; w < kWarps / kShares; ++w) {
-                    partner += ared[w * wstride + pl];
-                    cp += pred[w * 32 * P.B];
-                }
-                partner -= cp;
-#pragma unroll
-                for (int o = 1; o < kShares; o <<= 1) partner += __shfl_xor_sync(0xffffffffu, partner, o);
-                partner *= F::kInvUnit;
-            }
-            const bool store = h == 0 && tile < ntile && v < row_end && b < P.B && !failed;
-            if (store) {
+            mine = (mine - cm) * F::kInvUnit;
+            // the partner row (the up row of a gate row, the other half of a rotated pair) is the neighbouring row: the
+            // neighbouring lane, since passes begin at even rows
+            const float partner = __shfl_xor_sync(0xffffffffu, mine, 1);
+            if (tile < ntile && v < row_end && !failed) {
                 if (P.split_k == 1) epilogue<OutT>(P, b, v, mine, partner);
                 else P.partial[((size_t)split * P.B + b) * P.V + v] = mine;
             }
@@ -689,30 +672,32 @@ bool plan_stream(int bits, int B, int V, int groups, int split_k, int64_t rho, i
         pl.ok = !overrun;
         return pl;
     };
-    // rho is the number of CTAs per SM the row slabs are cut for (0: chosen here).
+    // The plan is chosen here; the caller's rho only reorders step (2) when it is negative (a tuning and test knob).
     // (1) If one CTA per SM covers its rows in a single pass of at most 32 rows inside half an SM's shared memory, do
     //     that and leave the SM's second CTA slot to the next launch of the stream, whose prologue and first copies
     //     then overlap this launch's arithmetic.
-    // (2) Otherwise a ring that keeps copies in flight during the arithmetic (two slots or more, or the whole slab in
-    //     one pass), tried in the order the caller's rho asks for: one CTA per SM with all of its shared memory
-    //     (32-row passes: two 16-row tiles per step, eight accumulation chains per warp), or two CTAs per SM with
-    //     half each (32- or 16-row passes).
+    // (2) Otherwise two CTAs per SM with half of its shared memory each, else one CTA per SM with all of it (measured:
+    //     16 warps per SM hide the MMA latency that 8 do not; rho < 0 tries one CTA per SM first): 32-row passes (two 16-row tiles per step, eight accumulation chains per warp)
+    //     with two ring slots or more; else, under two CTAs per SM, 32-row passes with one slot (the SM's other CTA
+    //     computes while this one's slot refills: measured 8 % faster than the next choice, whose passes cost the
+    //     same fixed work for half the rows); else 16-row passes with two slots or more.
     // (3) Otherwise one CTA per SM with a single slot, the K split raised until a slot fits.
     StreamPlan pick{};
     {
         const StreamPlan c = plan(sms, split, 32, kSmemCapTwo);
-        if (rho <= 2 && c.ok && c.npass == 1) pick = c;
+        if (c.ok && c.npass == 1) pick = c;
     }
     if (!pick.ok) {
-        const bool one_first = rho <= 1;
-        struct Try { int ctas; size_t cap; };
-        const Try one{sms, kSmemCap}, two{2 * sms, kSmemCapTwo};
+        const bool one_first = rho < 0;
+        struct Try { int ctas; size_t cap; bool one_slot; };
+        const Try one{sms, kSmemCap, false}, two{2 * sms, kSmemCapTwo, true};
         const Try tries[2] = {one_first ? one : two, one_first ? two : one};
-        for (int i = 0; i < 2 && !pick.ok; ++i)
-            for (int rpp : {32, 16}) {
-                const StreamPlan c = plan(tries[i].ctas, split, rpp, tries[i].cap);
-                if (c.ok && c.nbuf >= std::min(2, c.npass)) { pick = c; break; }
-            }
+        for (int i = 0; i < 2 && !pick.ok; ++i) {
+            const StreamPlan c32 = plan(tries[i].ctas, split, 32, tries[i].cap);
+            const StreamPlan c16 = plan(tries[i].ctas, split, 16, tries[i].cap);
+            if (c32.ok && (c32.nbuf >= std::min(2, c32.npass) || tries[i].one_slot)) pick = c32;
+            else if (c16.ok && c16.nbuf >= std::min(2, c16.npass)) pick = c16;
+        }
     }
     if (!pick.ok) {
         int sp = split;

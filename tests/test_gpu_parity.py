@@ -302,6 +302,23 @@ def test_ring_kernel_full_size_both_operand_forms(bits, B):
         _C.set_option(5, 0)
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("B", [1, 3, 8])
+@pytest.mark.parametrize("rho", [1, -1])
+@pytest.mark.parametrize("n,k", [(20000, 4096), (2100, 11008)])
+def test_ring_kernel_plans(bits, B, rho, n, k):
+    """Both orders of the ring kernel's plan search at sizes with several passes per CTA: two CTAs per SM with a single
+    32-row slot or 16-row passes (rho >= 0), one CTA per SM with a ring two to six slots deep (rho < 0); ragged last
+    slab and last pass."""
+    from crispybits_kernels import _C, packed_linear
+    plan = _C.decode_plan(bits, B, n, k, 1, rho, _C.sm_count())
+    assert plan is not None and (plan["passes"] >= 2 or k > 4096)
+    w, wd, bd = cached(n, k, bits, torch.float16, True, 31, 128, 0.02)
+    x = torch.randn(B, k, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(7 * B))
+    close(packed_linear(x, w, 1, rho, decode_threshold=8), ref_linear(x, wd, bd), torch.float16)
+    assert _C.decode_status() == 0
+
+
 def test_decode_status_word_is_clean_after_the_suite_so_far():
     from crispybits_kernels import _C
     assert _C.decode_status() == 0
