@@ -63,7 +63,7 @@ METRIC_STACK = "packed mixed-precision decode stack effective HBM bandwidth (Lla
 # dram__bytes_read + dram__bytes_write per W4 4096x4096 launch, from the ncu capture summarised under profiles/
 # (profiles/gemv_stream_w4_4096x4096_b1.md: the ring kernel's loads are one bulk copy per packed row plus the
 # scales and zeros, each byte once)
-NCU_TRAFFIC_W4 = 8977664
+NCU_TRAFFIC_W4 = 8979328
 L2_BYTES = 126e6
 
 

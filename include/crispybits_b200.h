@@ -89,8 +89,9 @@ const char* cb_version(void);
 /* Decode GEMV  out[B,n] = act(x[B,K] * W^T + bias).
  * Replaces packed_gemv_cuda (Crispybits/Kernel/csrc/packed_gemv.cu:252-269; bindings.cpp:33).
  * split_k >= 1 is clamped to ceil(K/32); rho is the number of resident CTAs per SM the grid is
- * sized for (0 = one CTA per work unit), as in host_utils.h:90-93.  scratch may be NULL when
- * split_k == 1. */
+ * sized for (0 = one CTA per work unit), as in host_utils.h:90-93: the shape-generic kernel uses it
+ * that way, the fp16 / bf16 ring kernel plans its own grid (see cb_decode_plan).  scratch may be NULL
+ * when split_k == 1. */
 int cb_packed_gemv(const void* x, int64_t B, const cb_weight* w, void* out,
                    int64_t K, int bits, int64_t group_size, int dtype,
                    int64_t split_k, int64_t rho, int act,

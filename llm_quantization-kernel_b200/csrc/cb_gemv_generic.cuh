@@ -22,22 +22,23 @@ constexpr int kGenericThreads = 256;
 static_assert(kGenericThreads / 32 * 2 == kTileN, "8 warps x 2 rows = one tile");
 
 // 32 consecutive activations starting at k0 as fp32, zero beyond K.  `vec` says rows of x start
-// 16-byte aligned, so whole chunks can use 128-bit loads.
+// 16-byte aligned, so whole chunks can use 128-bit loads.  x is read through L2 (ld.global.cg / volatile), never
+// through the non-coherent path: in a column-parallel stack peers store it while this grid may already be resident.
 template <typename T>
-__device__ __forceinline__ void load_x32(const T* __restrict__ xb, int k0, int K, bool vec, float (&xv)[32]) {
+__device__ __forceinline__ void load_x32(const T* xb, int k0, int K, bool vec, float (&xv)[32]) {
     if (vec && k0 + 32 <= K) {
         const uint4* p = reinterpret_cast<const uint4*>(xb + k0);
         if constexpr (std::is_same<T, float>::value) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const uint4 v = __ldg(p + i);
+                const uint4 v = __ldcg(p + i);
                 xv[4 * i + 0] = __uint_as_float(v.x); xv[4 * i + 1] = __uint_as_float(v.y);
                 xv[4 * i + 2] = __uint_as_float(v.z); xv[4 * i + 3] = __uint_as_float(v.w);
             }
         } else {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const uint4 v = __ldg(p + i);
+                const uint4 v = __ldcg(p + i);
                 const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int h = 0; h < 4; ++h) {
@@ -55,14 +56,14 @@ __device__ __forceinline__ void load_x32(const T* __restrict__ xb, int k0, int K
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
             const int k = k0 + j;
-            xv[j] = (k < K) ? to_f32(xb[k]) : 0.f;
+            xv[j] = (k < K) ? to_f32(*const_cast<const volatile T*>(xb + k)) : 0.f;
         }
     }
 }
 
 template <typename T, int BITS, int NB>
 __global__ void __launch_bounds__(kGenericThreads)
-gemv_generic_kernel(const T* __restrict__ x, const GemvParams P, const int xvec) {
+gemv_generic_kernel(const T* x, const GemvParams P, const int xvec) {
     __shared__ int s_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
