@@ -77,6 +77,8 @@ struct StreamParams {
     int grp_q, grp_r;      // group PAIRS per K-partition: quotient and remainder of (groups/2) / split_k
     unsigned off_red, off_xs, off_xsum, off_ring, off_bar;   // shared-memory carve-up
     int launch_kind;       // kLaunchPlain / kLaunchOrdered / kLaunchFree
+    int x_plane;           // bytes of one plane of staged activations: 16 * (groups of the largest partition) * B * 4
+    int red_bufs;          // copies of the reduction buffer: 2 (alternating with the pass) or 1 (a single pass)
 };
 
 // ---- small PTX wrappers ------------------------------------------------------------------------
@@ -145,7 +147,9 @@ template <bool BF> __device__ __forceinline__ float meta_f32(unsigned short bits
     else return __half2float(__ushort_as_half(bits));
 }
 
-constexpr int kXBlock = 80;   // bytes between staged activation blocks: 64 of data, 16 of padding (conflict-free 16-byte reads)
+// Staged activations: a block = the 64 bytes one (group, batch row, chunk) contributes, stored as four 16-byte pieces
+// in four planes (piece i of block j at i * plane + 16 * j): the lanes of a warp read and write consecutive 16-byte
+// pieces of one plane, which is conflict-free without padding.
 
 template <int BITS, int KIND>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -292,9 +296,10 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
                 if (F::shift(m) != 0) xf[m] = F::mul2(xf[m], F::pow2neg(F::shift(m)));
             }
             if (on) {
-                const uint32_t dst = s_xs + (uint32_t)(((gl * P.B + b) * 4 + tq) * kXBlock);
+                const uint32_t dst = s_xs + (uint32_t)(((gl * P.B + b) * 4 + tq) * 16);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) sts128(dst + 16 * i, make_uint4(xf[4 * i], xf[4 * i + 1], xf[4 * i + 2], xf[4 * i + 3]));
+                for (int i = 0; i < 4; ++i)
+                    sts128(dst + (uint32_t)(i * S.x_plane), make_uint4(xf[4 * i], xf[4 * i + 1], xf[4 * i + 2], xf[4 * i + 3]));
             }
             float x0 = (sa[0] + sb[0]) + (sc[0] + sd[0]), x1 = (sa[1] + sb[1]) + (sc[1] + sd[1]);
             float c0 = 0.f, c1 = 0.f;
@@ -330,8 +335,9 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
 
     // Lane (g, t) of the main loop supplies the MMA B fragments of batch row g: lanes without a batch row read zeros.
     const bool has_x = g < P.B;
-    const uint32_t x_lane0 = has_x ? s_xs + (uint32_t)(((wg_begin * P.B + g) * 4 + t) * kXBlock) : s_zero;
-    const uint32_t x_step = has_x ? (uint32_t)(P.B * 4 * kXBlock) : 0u;
+    const uint32_t x_lane0 = has_x ? s_xs + (uint32_t)(((wg_begin * P.B + g) * 4 + t) * 16) : s_zero;
+    const uint32_t x_step = has_x ? (uint32_t)(P.B * 4 * 16) : 0u;
+    const uint32_t x_plane = has_x ? (uint32_t)S.x_plane : 16u;      // (the zero block is 64 bytes: its pieces sit side by side)
     const uint32_t p8 = 8u * S.pitch, m8 = 8u * S.meta_stride;
     const int ngw = wg_end - wg_begin;
     int buf = 0;
@@ -340,7 +346,7 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
         const int row0 = row_begin + p * rpp;
         const int ntile = (min(rpp, row_end - row0) + 15) >> 4;
         const uint32_t slot = s_ring + (uint32_t)buf * S.slot_bytes;
-        float* myred = red + (size_t)(p & 1) * red_floats;
+        float* myred = red + (size_t)(p & (S.red_bufs - 1)) * red_floats;
         {   // bounded wait for this pass's rows
             int spins = 0;
             const uint32_t bar = s_bar + 8 * buf;
@@ -369,7 +375,7 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
             uint32_t xf[16];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const uint4 v = lds128(x_at + 16 * i);
+                const uint4 v = lds128(x_at + i * x_plane);
                 xf[4 * i] = v.x; xf[4 * i + 1] = v.y; xf[4 * i + 2] = v.z; xf[4 * i + 3] = v.w;
             }
             uint32_t wa[TILES][BITS], wb[TILES][BITS];
@@ -614,7 +620,7 @@ bool conflicts(const LaunchRec& a, const LaunchRec& b) {
 
 // Shared-memory layout of one CTA for K split `sp`, ring depth `nbuf` and `rpp` rows per pass; returns its size.
 // *overrun is set when a tile of the last ring slot would be read past the end of the allocation.
-size_t stream_layout(int bits, int B, int groups, int sp, int nbuf, int rpp, StreamParams& out, bool* overrun) {
+size_t stream_layout(int bits, int B, int groups, int sp, int nbuf, int rpp, int npass, StreamParams& out, bool* overrun) {
     const int gpairs = groups / 2;
     const int group_bytes = 16 * bits;
     const int ng = 2 * ((gpairs + sp - 1) / sp);                  // largest partition
@@ -629,10 +635,12 @@ size_t stream_layout(int bits, int B, int groups, int sp, int nbuf, int rpp, Str
     out.slot_bytes = rpp * (pitch + 2 * meta);
     out.off_ring = (unsigned)off; off += (size_t)nbuf * out.slot_bytes;
     off = (off + 127) & ~(size_t)127;
-    out.off_red = (unsigned)off; off += (size_t)2 * (kWarps * 2 * 8 * ((B + 1) / 2) * 4 + kWarps * 32 * B) * sizeof(float);
+    out.red_bufs = npass > 1 ? 2 : 1;                          // the reduction buffer alternates with the pass
+    out.off_red = (unsigned)off; off += (size_t)out.red_bufs * (kWarps * 2 * 8 * ((B + 1) / 2) * 4 + kWarps * 32 * B) * sizeof(float);
     out.off_xsum = (unsigned)off; off += (size_t)2 * groups * 8 * sizeof(float);
     off = (off + 127) & ~(size_t)127;
-    out.off_xs = (unsigned)off; off += (size_t)ng * B * 4 * kXBlock;   // staged activations of one partition
+    out.x_plane = ng * B * 4 * 16;
+    out.off_xs = (unsigned)off; off += (size_t)4 * out.x_plane;   // staged activations of one partition
     out.pitch = pitch; out.meta_stride = meta; out.nbuf = nbuf; out.rpp = rpp;
     const size_t tile_rows = (size_t)((rpp + 15) / 16) * 16;
     const size_t reach = (size_t)out.off_ring + (size_t)(nbuf - 1) * out.slot_bytes + tile_rows * pitch;
@@ -663,12 +671,12 @@ bool plan_stream(int bits, int B, int V, int groups, int split_k, int64_t rho, i
         // a slab shorter than a pass: the slot holds only the slab's rows (never fewer than 16: the scale reads of a
         // tile's absent rows then stay inside the slot's metadata)
         pl.rpp = std::max(16, std::min(rpp, rows_per_slab));
-        if (stream_layout(bits, B, groups, sp, 1, pl.rpp, tmp, &overrun) > cap || overrun) return pl;
-        pl.nslabs = nslabs;
         pl.npass = (rows_per_slab + pl.rpp - 1) / pl.rpp;
+        if (stream_layout(bits, B, groups, sp, 1, pl.rpp, pl.npass, tmp, &overrun) > cap || overrun) return pl;
+        pl.nslabs = nslabs;
         pl.nbuf = std::min(pl.npass, kMaxBuf);
-        while (pl.nbuf > 1 && (stream_layout(bits, B, groups, sp, pl.nbuf, pl.rpp, tmp, &overrun) > cap || overrun)) --pl.nbuf;
-        pl.smem = stream_layout(bits, B, groups, sp, pl.nbuf, pl.rpp, tmp, &overrun);
+        while (pl.nbuf > 1 && (stream_layout(bits, B, groups, sp, pl.nbuf, pl.rpp, pl.npass, tmp, &overrun) > cap || overrun)) --pl.nbuf;
+        pl.smem = stream_layout(bits, B, groups, sp, pl.nbuf, pl.rpp, pl.npass, tmp, &overrun);
         pl.ok = !overrun;
         return pl;
     };
@@ -731,7 +739,7 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
         P.counters = reinterpret_cast<int*>(scratch);
         P.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kCounterBytes);
     }
-    const size_t smem = stream_layout(BITS, P.B, P.groups, split, pick.nbuf, pick.rpp, S, nullptr);
+    const size_t smem = stream_layout(BITS, P.B, P.groups, split, pick.nbuf, pick.rpp, pick.npass, S, nullptr);
     P.split_k = split;
     S.g = P;
     S.nslabs = nslabs;
