@@ -56,6 +56,7 @@ constexpr int kMaxBuf = 6;
 constexpr int kSpinLimit = 1 << 22;           // bounded mbarrier wait (~ a second), then give up and flag
 constexpr size_t kSmemCap = 226 * 1024;       // one CTA per SM
 constexpr size_t kSmemCapTwo = 112 * 1024;    // two CTAs per SM
+constexpr size_t kSmemCapThree = 75 * 1024;   // three CTAs per SM (228 KB per SM, 1 KB reserved per CTA)
 
 __device__ int g_stream_status;               // 0 = ok; k > 0: the copy of pass k-1 never landed
 
@@ -151,8 +152,10 @@ template <bool BF> __device__ __forceinline__ float meta_f32(unsigned short bits
 // in four planes (piece i of block j at i * plane + 16 * j): the lanes of a warp read and write consecutive 16-byte
 // pieces of one plane, which is conflict-free without padding.
 
-template <int BITS, int KIND>
-__global__ void __launch_bounds__(kThreads, 2)
+// MINB = CTAs per SM the register allocation allows: 2 (up to 128 registers), or 3 (80 registers; a few spilled words)
+// for single-pass launches small enough that THREE consecutive launches of a stream fit an SM together.
+template <int BITS, int KIND, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
 gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
     // x is read with L2-coherent loads only (ld.global.cg): it is written while this grid is already resident, by the
     // previous kernel of the stream or, in a column-parallel stack, by peer GPUs.
@@ -748,8 +751,21 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
     S.grp_q = gpairs / split; S.grp_r = gpairs % split;
     const unsigned int grid = (unsigned)(nslabs * split);
 
-    static bool attr_done[64] = {};     // per device: the opt-in to large dynamic shared memory
-    auto kern = gemv_stream_kernel<BITS, KIND>;
+    // Which build of the kernel: a single-pass launch of at most a third of an SM's shared memory runs the one capped
+    // at 80 registers, so that three consecutive launches of a stream are resident per SM (measured at 4096x4096: W3
+    // 3.08 -> 2.93 us, W2 2.61 -> 2.23 us per launch; on multi-pass launches the capped build is 3-8 % slower, and a W4
+    // slab of 28 rows needs 78 KB).
+    using Kern = void (*)(const unsigned char*, const StreamParams);
+    Kern kern = gemv_stream_kernel<BITS, KIND, 2>;
+    int which = 0;
+    if constexpr (BITS != 4) {
+        if (pick.npass == 1 && smem <= kSmemCapThree) {
+            kern = gemv_stream_kernel<BITS, KIND, 3>;
+            which = 1;
+        }
+    }
+    static bool attr_done_all[2][64] = {};     // per build and device: the opt-in to large dynamic shared memory
+    bool* attr_done = attr_done_all[which];
     int dev = 0;
     CB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
