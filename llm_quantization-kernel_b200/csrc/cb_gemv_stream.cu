@@ -628,7 +628,7 @@ size_t stream_layout(int bits, int B, int groups, int sp, int nbuf, int rpp, int
     const int group_bytes = 16 * bits;
     const int ng = 2 * ((gpairs + sp - 1) / sp);                  // largest partition
     int meta = ng * 2;
-    meta += ((4 - meta) % 128 + 128) % 128;                        // rows 4 bytes apart (mod 128): conflict-free 2-byte reads
+    if ((meta / 4) % 2 == 0) meta += 4;                            // an odd number of banks from row to row: conflict-free 2-byte reads
     int pitch = ng * group_bytes;
     pitch += ((group_bytes - pitch) % 128 + 128) % 128;           // pitch == group_bytes (mod 128): conflict-free fragment reads
     size_t off = 0;
@@ -753,16 +753,13 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
 
     // Which build of the kernel: a single-pass launch of at most a third of an SM's shared memory runs the one capped
     // at 80 registers, so that three consecutive launches of a stream are resident per SM (measured at 4096x4096: W3
-    // 3.08 -> 2.93 us, W2 2.61 -> 2.23 us per launch; on multi-pass launches the capped build is 3-8 % slower, and a W4
-    // slab of 28 rows needs 78 KB).
+    // 3.08 -> 2.93 us, W2 2.61 -> 2.23 us per launch; on multi-pass launches the capped build is 3-8 % slower).
     using Kern = void (*)(const unsigned char*, const StreamParams);
     Kern kern = gemv_stream_kernel<BITS, KIND, 2>;
     int which = 0;
-    if constexpr (BITS != 4) {
-        if (pick.npass == 1 && smem <= kSmemCapThree) {
-            kern = gemv_stream_kernel<BITS, KIND, 3>;
-            which = 1;
-        }
+    if (pick.npass == 1 && smem <= kSmemCapThree) {
+        kern = gemv_stream_kernel<BITS, KIND, 3>;
+        which = 1;
     }
     static bool attr_done_all[2][64] = {};     // per build and device: the opt-in to large dynamic shared memory
     bool* attr_done = attr_done_all[which];
