@@ -751,28 +751,6 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
     S.grp_q = gpairs / split; S.grp_r = gpairs % split;
     const unsigned int grid = (unsigned)(nslabs * split);
 
-    // Which build of the kernel: a single-pass launch of at most a third of an SM's shared memory runs the one capped
-    // at 80 registers, so that three consecutive launches of a stream are resident per SM (measured at 4096x4096: W3
-    // 3.08 -> 2.93 us, W2 2.61 -> 2.23 us per launch; on multi-pass launches the capped build is 3-8 % slower).
-    using Kern = void (*)(const unsigned char*, const StreamParams);
-    Kern kern = gemv_stream_kernel<BITS, KIND, 2>;
-    int which = 0;
-    if (pick.npass == 1 && smem <= kSmemCapThree) {
-        kern = gemv_stream_kernel<BITS, KIND, 3>;
-        which = 1;
-    }
-    static bool attr_done_all[2][64] = {};     // per build and device: the opt-in to large dynamic shared memory
-    bool* attr_done = attr_done_all[which];
-    int dev = 0;
-    CB_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        CB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemCap));
-        // every decode kernel asks for the same shared-memory carve-out, so that consecutive launches of a stream
-        // never make an SM drain to re-partition its L1 / shared memory
-        CB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        if (dev >= 0 && dev < 64) attr_done[dev] = true;
-    }
-
     // Kind of this launch.  Inside stream capture: a follower if the capture's tail is this library's previous launch
     // on this stream, else the head of a new chain (ordered).  A follower runs free if its operands overlap those of
     // no launch since the chain's last ordered one, and that was at most kMaxUnordered - 1 launches ago.
@@ -804,6 +782,28 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
         S.launch_kind = free_run ? kLaunchFree : kLaunchOrdered;
         ++g_chain_counts[follower ? 1 : 0];
         if (follower) ++g_chain_counts[free_run ? 3 : 2];
+    }
+    // Which build of the kernel.  A FREE single-pass launch of at most a third of an SM's shared memory runs the build
+    // capped at 80 registers, so that three consecutive launches of the chain are resident per SM (measured at
+    // 4096x4096, independent launches: W4 2.80 -> 2.57 us, W3 3.08 -> 2.91, W2 2.61 -> 2.23).  The capped build itself is
+    // 3-8 % slower, so launches that wait for their predecessor anyway, and multi-pass launches, keep the other one.
+    using Kern = void (*)(const unsigned char*, const StreamParams);
+    Kern kern = gemv_stream_kernel<BITS, KIND, 2>;
+    int which = 0;
+    if (S.launch_kind == kLaunchFree && pick.npass == 1 && smem <= kSmemCapThree) {
+        kern = gemv_stream_kernel<BITS, KIND, 3>;
+        which = 1;
+    }
+    static bool attr_done_all[2][64] = {};     // per build and device: the opt-in to large dynamic shared memory
+    bool* attr_done = attr_done_all[which];
+    int dev = 0;
+    CB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        CB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemCap));
+        // every decode kernel asks for the same shared-memory carve-out, so that consecutive launches of a stream
+        // never make an SM drain to re-partition its L1 / shared memory
+        CB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
