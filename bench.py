@@ -15,8 +15,10 @@ than twice the 126 MB L2, so every launch streams its weights from HBM.  `value`
 bytes of all launches divided by the device time of the timed steps (CUDA events on the launching
 stream around CUDA-graph replays of a step, so Python launch overhead is not in the number).  `e2e`
 times the same GEMVs through the public API with the activations starting in pinned host memory and
-the result read back to the host every call; its `value` is the step captured on ONE stream (what a caller of
-packed_linear gets), the multi-stream and eager variants are reported beside it.  `roofline` describes the dominant kernel (the W4 GEMV):
+the results read back to the host: its `value` is the step captured on ONE stream with one copy of the step's
+activations in and one copy of the step's results out (what a decode loop does); the stricter constructions with
+copies around every call (one stream, five streams, eager) are reported beside it.  `reference_cuda` times the
+reference's own CUDA kernels (oracle/_ref, when built) on the same GPU with the same harness.  `roofline` describes the dominant kernel (the W4 GEMV):
 algorithmic bytes per launch over its average launch duration, against the measured HBM copy
 bandwidth in MEASURED_PEAKS.json.  `cpu_baseline` is the C oracle (OpenMP, all host threads) timed on
 a bounded sample of the same GEMVs on the host cores.
