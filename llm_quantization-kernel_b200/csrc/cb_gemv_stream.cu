@@ -652,7 +652,7 @@ size_t stream_layout(int bits, int B, int groups, int sp, int nbuf, int rpp, int
 }
 
 // The launch plan of the ring kernel: K split, row slabs, rows per pass, ring depth.  Pure host arithmetic.
-struct StreamPlan { int split, rpp, nbuf, nslabs, npass; size_t smem; bool ok; };
+struct StreamPlan { int split, rpp, nbuf, nslabs, npass; size_t smem; bool ok; bool three; };
 
 bool plan_stream(int bits, int B, int V, int groups, int split_k, int64_t rho, int sms, StreamPlan* out) {
     // K-partitions are whole PAIRS of groups (4-byte granularity of the metadata copies); the caller's
@@ -697,6 +697,14 @@ bool plan_stream(int bits, int B, int V, int groups, int split_k, int64_t rho, i
     {
         const StreamPlan c = plan(sms, split, 32, kSmemCapTwo);
         if (c.ok && c.npass == 1) pick = c;
+    }
+    if (!pick.ok && rho >= 0) {
+        // (1b) the same with two, then three CTAs per SM: every row of the matrix is in flight at once and no CTA loops.
+        //      Three per SM need the 80-register build and a third of the shared memory each.
+        const StreamPlan c2 = plan(2 * sms, split, 32, kSmemCapTwo);
+        const StreamPlan c3 = plan(3 * sms, split, 32, kSmemCapThree);
+        if (c2.ok && c2.npass == 1) pick = c2;
+        else if (c3.ok && c3.npass == 1) { pick = c3; pick.three = true; }
     }
     if (!pick.ok) {
         const bool one_first = rho < 0;
@@ -785,12 +793,13 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
     }
     // Which build of the kernel.  A FREE single-pass launch of at most a third of an SM's shared memory runs the build
     // capped at 80 registers, so that three consecutive launches of the chain are resident per SM (measured at
-    // 4096x4096, independent launches: W4 2.80 -> 2.57 us, W3 3.08 -> 2.91, W2 2.61 -> 2.23).  The capped build itself is
-    // 3-8 % slower, so launches that wait for their predecessor anyway, and multi-pass launches, keep the other one.
+    // 4096x4096, independent launches: W4 2.80 -> 2.57 us, W3 3.08 -> 2.91, W2 2.61 -> 2.23); so does a plan that puts
+    // three CTAs of ONE launch on every SM (11008x4096 W4: 8.0 -> 7.1 us).  The capped build itself is 3-8 % slower, so
+    // launches that wait for their predecessor anyway, and multi-pass launches, keep the other one.
     using Kern = void (*)(const unsigned char*, const StreamParams);
     Kern kern = gemv_stream_kernel<BITS, KIND, 2>;
     int which = 0;
-    if (S.launch_kind == kLaunchFree && pick.npass == 1 && smem <= kSmemCapThree) {
+    if ((S.launch_kind == kLaunchFree && pick.npass == 1 && smem <= kSmemCapThree) || pick.three) {
         kern = gemv_stream_kernel<BITS, KIND, 3>;
         which = 1;
     }
