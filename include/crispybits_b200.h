@@ -228,7 +228,7 @@ size_t cb_gemv_scratch_bytes(int64_t B, int64_t V, int64_t split_k);
  * streamlined decode kernel, value 0/1 (default 1, or 0 when CRISPYBITS_PDL=0 is in the environment).
  * With it on, a decode call may start fetching PACKED WEIGHTS before the previous kernel of the
  * stream has finished; activations, outputs and scratch are only touched afterwards.  option 1:
- * value 1 forces the shape-generic decode kernel everywhere (for A/B checks).  option 2: unused.  option 3: which tcgen05 prefill kernel -- 0 (default) by M, 1 the kernel with both
+ * value 1 forces the shape-generic decode kernel everywhere (for A/B checks).  option 2: unused.  option 3: which tcgen05 prefill kernel -- 0 (default) the one with fewer estimated waves over the SMs, 1 the kernel with both
  * operands in shared memory (128-token tiles), 2 the kernel with the expanded weights in tensor memory
  * (256-token tiles).  option 4: chains of captured decode launches (see cb_chain_stats), value 0/1, default 1.
  * option 5: operand form of the fp16 ring kernel -- 0 (default) packed fields used as fp16 subnormals, 1 fields

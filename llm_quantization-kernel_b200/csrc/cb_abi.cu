@@ -406,19 +406,33 @@ int cb_packed_gemm_scratch(const void* x, int64_t M, const cb_weight* w, void* o
     CB_REQUIRE(out != nullptr, "packed_gemm: out is NULL");
     CB_REQUIRE(M < (1ll << 30), "packed_gemm: M out of range");
     if (use_tensor_cores && !g_force_generic) {
-        // tcgen05 kernels when the problem is inside their domain (-1 = it is not): above 128 tokens, for bf16, and
-        // wherever it can split K over otherwise idle SMs, the one that keeps the expanded weights in tensor memory
-        // and serves 256 tokens per expansion; else the 128-token one
-        const bool splits = scratch != nullptr && gemm_ws_splits(M, w->n, K) > 1 &&
-                            scratch_bytes >= (size_t)2 * M * w->n * sizeof(float);
-        const bool ws_first = g_gemm_kernel == 2 || (g_gemm_kernel == 0 && (M > 128 || dtype == CB_BF16 || splits));
-        if (ws_first) {
-            const int rc3 = launch_gemm_ws(dtype, x, M, w, out, K, bits, group_size, act, reinterpret_cast<cudaStream_t>(stream),
-                                           scratch, scratch_bytes);
-            if (rc3 != -1) return rc3;
+        // tcgen05 kernels when the problem is inside their domain (-1 = it is not).  Two tilings: the weight-stationary
+        // kernel (128 weight rows x 256 tokens per tile, expanded weights in tensor memory, K split over idle SMs when
+        // the caller brought scratch; fp16 and bf16) and the shared-memory-operand kernel (256 weight rows x 128 tokens;
+        // fp16).  Both run one tile per SM and wave, so the choice is by waves: measured per wave at K = 4096, 33 us for
+        // the first and 46 us for the second, plus ~5 us for the reduction of a K split.
+        const int sms = sm_count_current();
+        const int64_t N = w->n;
+        const int sp_all = gemm_ws_splits(M, N, K);
+        const int sp = (scratch != nullptr && sp_all > 1 && scratch_bytes >= (size_t)sp_all * M * N * sizeof(float)) ? sp_all : 1;
+        bool ws_first = true;
+        if (g_gemm_kernel == 1) ws_first = false;
+        else if (g_gemm_kernel == 0 && dtype == CB_F16 && sms > 0) {
+            const int64_t ws_items = ((M + 255) / 256) * ((N + 127) / 128) * sp;
+            const int64_t tc_tiles = ((M + 127) / 128) * ((N + 255) / 256);
+            const double kscale = (double)K / 4096.0;
+            const double t_ws = (double)((ws_items + sms - 1) / sms) * 33.0 * kscale / sp + (sp > 1 ? 5.0 : 0.0);
+            const double t_tc = (double)((tc_tiles + sms - 1) / sms) * 46.0 * kscale;
+            ws_first = t_ws <= t_tc;
         }
-        const int rc2 = launch_gemm_tc(dtype, x, M, w, out, K, bits, group_size, act, reinterpret_cast<cudaStream_t>(stream));
-        if (rc2 != -1) return rc2;
+        for (int attempt = 0; attempt < 2; ++attempt) {
+            const bool use_ws = (attempt == 0) == ws_first;
+            const int rc2 = use_ws ? launch_gemm_ws(dtype, x, M, w, out, K, bits, group_size, act,
+                                                    reinterpret_cast<cudaStream_t>(stream), scratch, scratch_bytes)
+                                   : launch_gemm_tc(dtype, x, M, w, out, K, bits, group_size, act,
+                                                    reinterpret_cast<cudaStream_t>(stream));
+            if (rc2 != -1) return rc2;
+        }
     }
     const int round_w = (use_tensor_cores && dtype != CB_F32) ? 1 : 0;
     return launch_gemm_simt(dtype, x, M, w, out, K, bits, group_size, act, round_w,
