@@ -2,7 +2,7 @@
 """Compile the reference's own CUDA extension (its three translation units, unmodified, read where they lie in the
 read-only reference tree) into oracle/_ref/crispybits_ref_C.so for sm_100a.  TEST / BASELINE INFRASTRUCTURE ONLY.
 
-    python oracle/build_ref_cuda.py [/root/reference]
+    python oracle/build_ref_cuda.py [path/to/reference]        (default: $CRISPYBITS_REFERENCE, else the tree beside the build)
 
 The sources are Crispybits/Kernel/csrc/{bindings.cpp, packed_gemv.cu, packed_gemm.cu} (the list of the reference's
 Crispybits/Kernel/setup.py:11-16, with its flags -O3 -std=c++17 -lineinfo); they are compiled with torch's generic
@@ -17,10 +17,16 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 NAME = "crispybits_ref_C"
+REF_ROOT = os.environ.get("CRISPYBITS_REFERENCE", os.path.join(os.sep, "root", "reference"))
 
 
-def build(ref_root="/root/reference", verbose=False):
-    src = os.path.join(ref_root, "Crispybits", "Kernel", "csrc")
+def sources_present(ref_root=None):
+    """True when the reference tree with its CUDA sources is on this machine."""
+    return os.path.isdir(os.path.join(ref_root or REF_ROOT, "Crispybits", "Kernel", "csrc"))
+
+
+def build(ref_root=None, verbose=False):
+    src = os.path.join(ref_root or REF_ROOT, "Crispybits", "Kernel", "csrc")
     files = [os.path.join(src, f) for f in ("bindings.cpp", "packed_gemv.cu", "packed_gemm.cu")]
     if not all(os.path.exists(f) for f in files):
         raise FileNotFoundError(f"reference sources not found under {src}")
@@ -47,4 +53,4 @@ def load_module():
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", verbose=True))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None, verbose=True))
