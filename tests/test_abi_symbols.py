@@ -69,6 +69,8 @@ def test_decode_plan_is_host_arithmetic_and_stays_inside_an_sm():
                             if grid > sms and split == 1:
                                 assert smem <= 112 * 1024
                                 seen_two_per_sm = True
+                            if grid > 2 * sms and split == 1:
+                                assert smem <= 75 * 1024 and passes == 1, "three CTAs per SM: a third of the shared memory, one pass"
     assert seen_two_per_sm
     # outside the kernel's domain: K not a multiple of 256, batch above 8
     assert lib.cb_decode_plan(4, 1, 4096, 4096 + 128, 1, 1, 148, out) != 0
