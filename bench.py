@@ -50,7 +50,7 @@ import torch  # noqa: E402
 
 N_OUT, K_IN, GROUP = 4096, 4096, 128
 BITS = (4, 3, 2)
-COPIES = 48                 # distinct weight matrices per bit-width and step (about 1 GB in all)
+COPIES = 96                 # distinct weight matrices per bit-width and step (about 2 GB in all; a 7B decode step is 128 launches)
 E2E_STREAMS = 5             # streams the end-to-end step is pipelined over
 FALLBACK_HBM_GBS = 6650.0   # used only without MEASURED_PEAKS.json
 FALLBACK_TFLOPS = 1590.0
@@ -496,7 +496,7 @@ def run_gemv_workload(args, rank, world, device, barrier, reduce_max):
            "pipelined_graph_value": None if piped_ms is None else gbs(piped_ms),
            "api": "crispybits_kernels.packed_linear; packed weights resident on the device as in install_bitmap.  value = "
                   "step_copies_graph_value: per step one copy of all calls' activations from pinned host memory, the "
-                  "step's 144 calls (each on its own row) on one stream, one copy of all results back to pinned host "
+                  f"step's {3 * COPIES} calls (each on its own row) on one stream, one copy of all results back to pinned host "
                   "memory, captured in a CUDA graph and replayed.  one_stream_graph_value: x copied in and y copied "
                   "back around EVERY call, same stream, captured; eager_value: that per-call step issued call by call "
                   f"from Python; pipelined_graph_value: the per-call step captured over {E2E_STREAMS} streams.  All "

@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 from typing import Dict, List, Tuple
 
 import torch
@@ -150,6 +151,29 @@ def _weight(packed, scales, zeros, bias) -> _Weight:
     return _Weight(packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(), _ptr(bias), packed.shape[0])
 
 
+# Weights that passed their checks, so that a model's repeated calls with the same tensors do not pay for them again:
+# (identities of the four tensors, bits, K, group size, activation dtype and device) -> (weak reference to `packed`,
+# the record handed to the library).  An identity can be reused after a tensor dies, hence the weak reference; a tensor
+# whose storage is swapped in place (`.data = ...`) changes its data pointer, which is compared too.
+_checked: Dict[tuple, tuple] = {}
+
+
+def _checked_weight(x, packed, scales, zeros, bias, bits: int, k: int, gs: int, name: str) -> _Weight:
+    key = (id(packed), id(scales), id(zeros), id(bias), bits, k, gs, x.dtype, x.device)
+    hit = _checked.get(key)
+    if hit is not None and hit[0]() is packed and hit[1].packed == packed.data_ptr():
+        return hit[1]
+    _check_weight(x, packed, scales, zeros, bits, k, gs, name)
+    w = _weight(packed, scales, zeros, _bias_or_none(bias, x, packed.shape[0]))
+    if len(_checked) >= 8192:
+        _checked.clear()
+    _checked[key] = (weakref.ref(packed), w)
+    return w
+
+
+_COUNTER_REGION = 65536 * 4      # cb_gemv_scratch_bytes: a fixed region of arrival counters, then split_k * B * V floats
+
+
 # Split-K scratch: one zero-initialised buffer per (device, stream), grown on demand and kept alive
 # for the life of the process (CUDA graphs that captured its address stay valid).  The kernels reset
 # the counters they use, so the buffer is zeroed only when it is created.
@@ -172,8 +196,26 @@ def _scratch_for(x: torch.Tensor, stream: int, nbytes: int):
 
 def _decode_scratch(x, stream: int, B: int, V: int, pk: int):
     """Scratch for a decode call.  Sized for the requested split and, so that the streamlined kernel may
-    raise the split when its shared-memory budget asks for it, for at least a 4-way split."""
-    return _scratch_for(x, stream, max(_lib.cb_gemv_scratch_bytes(B, V, pk), _lib.cb_gemv_scratch_bytes(B, V, 4)))
+    raise the split when its shared-memory budget asks for it, for at least a 4-way split (the arithmetic of
+    cb_gemv_scratch_bytes, done here to save two library calls per launch)."""
+    return _scratch_for(x, stream, _COUNTER_REGION + max(pk, 4) * B * V * 4)
+
+
+class _on_device:
+    """`with torch.cuda.device(...)` only when the tensor's device is not the current one."""
+    __slots__ = ("ctx",)
+
+    def __init__(self, device):
+        self.ctx = None if device.index is None or torch.cuda.current_device() == device.index else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            return self.ctx.__exit__(*exc)
+        return False
 
 
 def _stream(x) -> int:
@@ -183,22 +225,20 @@ def _stream(x) -> int:
 def packed_gemv(x, packed, scales, zeros, bias, bits, in_features, group_size, split_k, rho, act, workspace):
     bits, k, gs, split_k, rho, act = int(bits), int(in_features), int(group_size), int(split_k), int(rho), int(act)
     _check_x(x, k)
-    _check_weight(x, packed, scales, zeros, bits, k, gs, "packed_gemv")
+    w = _checked_weight(x, packed, scales, zeros, bias, bits, k, gs, "packed_gemv")
     if split_k < 1:
         _fail("split_k must be >= 1")
     if not 0 <= act <= 2:
         _fail("act must be 0 (none), 1 (relu) or 2 (silu)")
-    bias = _bias_or_none(bias, x, packed.shape[0])
     _check_workspace(workspace, x)
     B, n = x.shape[0], packed.shape[0]
     out = torch.empty((B, n), dtype=x.dtype, device=x.device)
     if B == 0:
         return out
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         st = _stream(x)
         pk = max(1, min(split_k, -(-k // 32)))
         sc = _decode_scratch(x, st, B, n, pk)
-        w = _weight(packed, scales, zeros, bias)
         _rc(_lib.cb_packed_gemv(x.data_ptr(), B, ctypes.byref(w), out.data_ptr(), k, bits, gs, _DTYPE[x.dtype],
                                 pk, rho, act, _ptr(sc), 0 if sc is None else sc.numel(), st))
     return out

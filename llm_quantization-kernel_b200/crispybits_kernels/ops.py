@@ -85,9 +85,19 @@ class PackedLinearWeight:
                        zeros=mv(self.zeros, dtype), bias=None if self.bias is None else mv(self.bias, dtype))
 
 
+_ABSENT = {}       # (device, dtype) -> the 0-element tensor that stands for "absent"; made once, not per call
+
+
+def _absent(device, dtype) -> torch.Tensor:
+    t = _ABSENT.get((device, dtype))
+    if t is None:
+        t = _ABSENT[(device, dtype)] = torch.empty(0, device=device, dtype=dtype)
+    return t
+
+
 def _none_like(x: torch.Tensor) -> torch.Tensor:
     """The bindings take a 0-element tensor for "absent" (ops.py:74-83)."""
-    return torch.empty(0, device=x.device, dtype=x.dtype)
+    return _absent(x.device, x.dtype)
 
 
 def _bias_arg(w: PackedLinearWeight, x: torch.Tensor):
@@ -95,7 +105,7 @@ def _bias_arg(w: PackedLinearWeight, x: torch.Tensor):
 
 
 def _ws_arg(workspace, x):
-    return torch.empty(0, device=x.device, dtype=torch.int32) if workspace is None else workspace
+    return _absent(x.device, torch.int32) if workspace is None else workspace
 
 
 def new_workspace(device) -> torch.Tensor:
@@ -249,6 +259,8 @@ def _resolve(split_k: Optional[int], rho: int, batch: int, v_rows: int, k: int, 
 
 # ------------------------------------------------------------------ operators
 def _rows(x: torch.Tensor) -> torch.Tensor:
+    if x.dim() == 2 and x.is_contiguous():
+        return x
     return x.reshape(-1, x.shape[-1]).contiguous()
 
 
@@ -264,7 +276,7 @@ def _packed_linear_raw(x, w, split_k=None, rho=1, act=None, decode_threshold=DEC
     else:
         y = _C.packed_gemm(x2, w.packed, w.scales, w.zeros, _bias_arg(w, x2), w.bits, w.in_features,
                            w.group_size, code, use_tensor_cores)
-    return y.reshape(*lead, w.out_features)
+    return y if len(lead) == 1 else y.reshape(*lead, w.out_features)
 
 
 def packed_linear(x: torch.Tensor, w: PackedLinearWeight, split_k: Optional[int] = None, rho: int = 1,
