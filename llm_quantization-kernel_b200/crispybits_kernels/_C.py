@@ -154,15 +154,18 @@ def _weight(packed, scales, zeros, bias) -> _Weight:
 # Weights that passed their checks, so that a model's repeated calls with the same tensors do not pay for them again:
 # (identities of the four tensors, bits, K, group size, activation dtype and device) -> (weak reference to `packed`,
 # the record handed to the library).  An identity can be reused after a tensor dies, hence the weak reference; a tensor
-# whose storage is swapped in place (`.data = ...`) changes its data pointer, which is compared too.
+# whose storage is swapped in place (`.data = ...`) changes its data pointer, so the four pointers are compared too.
 _checked: Dict[tuple, tuple] = {}
 
 
 def _checked_weight(x, packed, scales, zeros, bias, bits: int, k: int, gs: int, name: str) -> _Weight:
     key = (id(packed), id(scales), id(zeros), id(bias), bits, k, gs, x.dtype, x.device)
     hit = _checked.get(key)
-    if hit is not None and hit[0]() is packed and hit[1].packed == packed.data_ptr():
-        return hit[1]
+    if hit is not None and hit[0]() is packed:
+        w = hit[1]
+        if (w.packed == packed.data_ptr() and w.scales == scales.data_ptr() and w.zeros == zeros.data_ptr()
+                and (w.bias or 0) == _ptr(bias)):
+            return w
     _check_weight(x, packed, scales, zeros, bits, k, gs, name)
     w = _weight(packed, scales, zeros, _bias_or_none(bias, x, packed.shape[0]))
     if len(_checked) >= 8192:

@@ -319,6 +319,25 @@ def test_ring_kernel_plans(bits, B, rho, n, k):
     assert _C.decode_status() == 0
 
 
+def test_remembered_weight_checks_follow_the_tensors():
+    """The shim remembers weights that passed their checks by tensor identity.  Swapping a tensor's storage in place, or
+    passing a bad tensor after good ones, must not be served from that memory."""
+    from dataclasses import replace
+    from crispybits_kernels import packed_linear
+    w, wd, _ = cached(256, 512, 4, torch.float16, False, 77)
+    x = torch.randn(1, 512, device=DEV, dtype=torch.float16, generator=torch.Generator(DEV).manual_seed(2))
+    w = replace(w, scales=w.scales.clone())                       # own tensors: this test changes them
+    y0 = packed_linear(x, w)
+    close(y0, ref_linear(x, wd), torch.float16)
+    assert torch.equal(packed_linear(x, w), y0)                   # second call: served from the remembered record
+    w.scales.data = (w.scales * 2).contiguous()                   # same Python object, new storage
+    close(packed_linear(x, w), 2 * ref_linear(x, wd), torch.float16)
+    with pytest.raises(RuntimeError):
+        packed_linear(x, replace(w, scales=w.scales.float()))     # metadata dtype must match x
+    with pytest.raises(RuntimeError):
+        packed_linear(x, replace(w, packed=w.packed[:, :-1].contiguous()))
+
+
 def test_decode_status_word_is_clean_after_the_suite_so_far():
     from crispybits_kernels import _C
     assert _C.decode_status() == 0
