@@ -60,6 +60,9 @@ COMM_TEXT = {
     "p2p": "all-gather fused into the decode kernel: peer stores over NVLink and an in-kernel rank hand-shake",
     "p2p_barrier": "all-gather fused into the decode kernel's epilogue as peer stores over NVLink, "
                    "one-CTA flag barrier kernel (programmatic dependent launch) after each launch",
+    "p2p_seq": "all-gather fused into the decode kernel's epilogue as peer stores over NVLink; launches numbered within "
+               "the step, each waits in the kernel for its predecessor's flag from every rank (no completion event on its "
+               "own GPU), a one-CTA kernel after each launch publishes its completion",
 }
 METRIC_STACK = "packed mixed-precision decode stack effective HBM bandwidth (Llama-2-7B shapes, 32 blocks)"
 # dram__bytes_read + dram__bytes_write per W4 4096x4096 launch, from the ncu capture summarised under profiles/
@@ -970,7 +973,7 @@ def main():
     ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM figures")
     ap.add_argument("--no-sweeps", action="store_true", help="skip the decode sweep and the fused decode figures")
     ap.add_argument("--no-stack", action="store_true", help="skip the decode-stack figures")
-    ap.add_argument("--comm", default="p2p_barrier", choices=["nccl", "p2p", "p2p_barrier"],
+    ap.add_argument("--comm", default="p2p_seq", choices=["nccl", "p2p", "p2p_barrier", "p2p_seq"],
                     help="how the column-parallel stack gathers its activations at N > 1")
     ap.add_argument("--batch", type=int, default=1, help="decode batch of the stack workload (1..8)")
     args = ap.parse_args()

@@ -78,6 +78,7 @@ typedef struct cb_scatter {
     void* epoch;
     void* done;
     int* status;
+    int64_t seq;
 } cb_scatter;
 
 /* Message of the last error raised on this thread ("" if none). */
@@ -144,6 +145,19 @@ int cb_peer_barrier(void* const* peer_flags, void* my_flags, void* epoch, int* s
  * needs before it reads a gathered buffer.  `scatter` supplies world, my_flags, epoch and status.  New for the
  * multi-GPU stack. */
 int cb_peer_wait(const cb_scatter* scatter, void* stream);
+
+/* Numbered hand-shake (scatter->sync == 2), the cheapest of the three: the launches of a step are numbered seq = 0,
+ * 1, ... in issue order, identically on every rank.  A scatter launch with seq > 0 waits in the kernel (bounded) until
+ * every rank has published seq completed launches of the running step (flag >= *epoch + seq; `epoch`, a zeroed uint32
+ * in this rank's memory, counts the launches of all finished steps) and does not wait for its predecessor's completion
+ * on this GPU; the launch with seq == 0 is an ordinary serialised launch and reads the step's input.  After EVERY
+ * scatter launch call cb_peer_publish with the same seq: a one-CTA kernel that is released by the launch's completion
+ * and stores *epoch + seq + 1 into every rank's flag array.  After the step's last publish call cb_peer_step_end with
+ * the number of launches: it waits (bounded) until every rank has published all of them -- the result is then
+ * complete here and no peer touches the step's buffers any more -- and advances *epoch.  `done` is not used.  Buffers
+ * may be reused as with sync == 1.  New for the multi-GPU stack. */
+int cb_peer_publish(const cb_scatter* scatter, void* stream);
+int cb_peer_step_end(const cb_scatter* scatter, int64_t launches, void* stream);
 
 /* Prefill GEMM  out[M,n] = act(x[M,K] * Wdq^T + bias), float32 accumulation.
  * Replaces packed_gemm_cuda (Crispybits/Kernel/csrc/packed_gemm.cu:182-203; bindings.cpp:34).

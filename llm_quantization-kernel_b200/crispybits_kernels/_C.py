@@ -345,7 +345,7 @@ class _Scatter(ctypes.Structure):
     """struct cb_scatter of include/crispybits_b200.h"""
     _fields_ = [("peer_out", _vp * 8), ("world", _int), ("n_gather", _i64), ("ld", _i64), ("col", _i64),
                 ("sync", _int), ("rank", _int), ("peer_flags", _vp * 8), ("my_flags", _vp), ("epoch", _vp),
-                ("done", _vp), ("status", _vp)]
+                ("done", _vp), ("status", _vp), ("seq", _i64)]
 
 
 class PeerSync:
@@ -353,9 +353,10 @@ class PeerSync:
     launch count, CTA counter and status."""
 
     def __init__(self, peer_flag_ptrs, my_flags: torch.Tensor, epoch: torch.Tensor, done: torch.Tensor,
-                 status: torch.Tensor, rank: int):
+                 status: torch.Tensor, rank: int, numbered: bool = False):
         self.peer_flag_ptrs, self.rank = list(peer_flag_ptrs), int(rank)
         self.my_flags, self.epoch, self.done, self.status = my_flags, epoch, done, status
+        self.numbered = bool(numbered)     # the numbered hand-shake (cb_scatter.sync == 2): seq per launch, publish, step end
 
 
 _SP = ctypes.POINTER(_Scatter)
@@ -363,17 +364,20 @@ _lib.cb_packed_gemv_scatter.argtypes = [_vp, _i64, _WP, _vp, _SP, _i64, _int, _i
 _lib.cb_fused_gate_up_scatter.argtypes = [_vp, _i64, _WP, _WP, _vp, _SP, _i64, _int, _i64, _int, _i64, _i64, _vp, _sz, _vp]
 _lib.cb_peer_barrier.argtypes = [ctypes.POINTER(_vp), _vp, _vp, _vp, _int, _int, _vp]
 _lib.cb_peer_wait.argtypes = [_SP, _vp]
-for _f in ("cb_packed_gemv_scatter", "cb_fused_gate_up_scatter", "cb_peer_barrier", "cb_peer_wait"):
+_lib.cb_peer_publish.argtypes = [_SP, _vp]
+_lib.cb_peer_step_end.argtypes = [_SP, _i64, _vp]
+for _f in ("cb_packed_gemv_scatter", "cb_fused_gate_up_scatter", "cb_peer_barrier", "cb_peer_wait", "cb_peer_publish",
+           "cb_peer_step_end"):
     getattr(_lib, _f).restype = _int
 
 
-def _scatter(peer_ptrs, n_gather: int, ld: int, col: int, sync: "PeerSync | None" = None) -> _Scatter:
+def _scatter(peer_ptrs, n_gather: int, ld: int, col: int, sync: "PeerSync | None" = None, seq: int = 0) -> _Scatter:
     sc = _Scatter()
     for i, ptr in enumerate(peer_ptrs):
         sc.peer_out[i] = ptr
     sc.world, sc.n_gather, sc.ld, sc.col = len(peer_ptrs), n_gather, ld, col
     if sync is not None:
-        sc.sync, sc.rank = 1, sync.rank
+        sc.sync, sc.rank, sc.seq = (2 if sync.numbered else 1), sync.rank, int(seq)
         for i, ptr in enumerate(sync.peer_flag_ptrs):
             sc.peer_flags[i] = ptr
         sc.my_flags, sc.epoch = sync.my_flags.data_ptr(), sync.epoch.data_ptr()
@@ -382,9 +386,10 @@ def _scatter(peer_ptrs, n_gather: int, ld: int, col: int, sync: "PeerSync | None
 
 
 def packed_gemv_scatter(x, packed, scales, zeros, bias, out, peer_ptrs, n_gather, ld, col, bits, in_features,
-                        group_size, split_k, rho, act, sync=None):
+                        group_size, split_k, rho, act, sync=None, seq=0):
     """packed_gemv whose output rows < n_gather go to every rank's gathered buffer (peer pointers) at column
-    `col` of a [B, ld] matrix; the other rows go to `out` [B, N]."""
+    `col` of a [B, ld] matrix; the other rows go to `out` [B, N].  `seq`: number of the launch within its step, for a
+    numbered hand-shake."""
     bits, k, gs, split_k = int(bits), int(in_features), int(group_size), int(split_k)
     _check_x(x, k)
     _check_weight(x, packed, scales, zeros, bits, k, gs, "packed_gemv_scatter")
@@ -396,14 +401,14 @@ def packed_gemv_scatter(x, packed, scales, zeros, bias, out, peer_ptrs, n_gather
         st = _stream(x)
         pk = max(1, min(split_k, -(-k // 32)))
         sc = _decode_scratch(x, st, B, n, pk)
-        w, s = _weight(packed, scales, zeros, bias), _scatter(peer_ptrs, int(n_gather), int(ld), int(col), sync)
+        w, s = _weight(packed, scales, zeros, bias), _scatter(peer_ptrs, int(n_gather), int(ld), int(col), sync, seq)
         _rc(_lib.cb_packed_gemv_scatter(x.data_ptr(), B, ctypes.byref(w), out.data_ptr(), ctypes.byref(s), k, bits, gs,
                                         _DTYPE[x.dtype], pk, int(rho), int(act), _ptr(sc), 0 if sc is None else sc.numel(), st))
     return out
 
 
 def fused_gate_up_scatter(x, wg, sg, zg, wu, su, zu, out, peer_ptrs, n_gather, ld, col, bits, in_features, group_size,
-                          split_k, rho, sync=None):
+                          split_k, rho, sync=None, seq=0):
     bits, k, gs, split_k = int(bits), int(in_features), int(group_size), int(split_k)
     _check_x(x, k)
     _check_weight(x, wg, sg, zg, bits, k, gs, "fused_gate_up_scatter(gate)")
@@ -417,7 +422,7 @@ def fused_gate_up_scatter(x, wg, sg, zg, wu, su, zu, out, peer_ptrs, n_gather, l
         st = _stream(x)
         pk = max(1, min(split_k, -(-k // 32)))
         sc = _decode_scratch(x, st, B, 2 * n, pk)
-        g, u, s = _weight(wg, sg, zg, None), _weight(wu, su, zu, None), _scatter(peer_ptrs, int(n_gather), int(ld), int(col), sync)
+        g, u, s = _weight(wg, sg, zg, None), _weight(wu, su, zu, None), _scatter(peer_ptrs, int(n_gather), int(ld), int(col), sync, seq)
         _rc(_lib.cb_fused_gate_up_scatter(x.data_ptr(), B, ctypes.byref(g), ctypes.byref(u), out.data_ptr(), ctypes.byref(s),
                                           k, bits, gs, _DTYPE[x.dtype], pk, int(rho), _ptr(sc), 0 if sc is None else sc.numel(), st))
     return out
@@ -430,6 +435,20 @@ def peer_barrier(peer_flag_ptrs, my_flags: torch.Tensor, epoch: torch.Tensor, st
     with torch.cuda.device(my_flags.device):
         _rc(_lib.cb_peer_barrier(arr, my_flags.data_ptr(), epoch.data_ptr(), status.data_ptr(), world, int(rank),
                                  torch.cuda.current_stream(my_flags.device).cuda_stream))
+
+
+def peer_publish(sync: "PeerSync", seq: int):
+    """Numbered hand-shake: after scatter launch `seq` of a step, the one-CTA kernel that tells every rank it is done."""
+    sc = _scatter([0] * len(sync.peer_flag_ptrs), 0, 1, 0, sync, seq)
+    with _on_device(sync.my_flags.device):
+        _rc(_lib.cb_peer_publish(ctypes.byref(sc), torch.cuda.current_stream(sync.my_flags.device).cuda_stream))
+
+
+def peer_step_end(sync: "PeerSync", launches: int):
+    """Numbered hand-shake: end of a step of `launches` launches (bounded wait for every rank, then the step base moves)."""
+    sc = _scatter([0] * len(sync.peer_flag_ptrs), 0, 1, 0, sync)
+    with _on_device(sync.my_flags.device):
+        _rc(_lib.cb_peer_step_end(ctypes.byref(sc), int(launches), torch.cuda.current_stream(sync.my_flags.device).cuda_stream))
 
 
 def peer_wait(sync: "PeerSync"):

@@ -17,7 +17,9 @@ each launch; `comm="p2p"` fuses the gather into the decode kernel -- every outpu
 straight into all ranks' peer-mapped activation buffers, and the kernel itself waits for its peers before
 it reads its activations and publishes its completion to them, so a block is four launches and nothing
 else; `comm="p2p_barrier"` keeps the stores but separates the hand-shake into a one-CTA barrier kernel
-after each launch.
+after each launch; `comm="p2p_seq"` numbers the launches of a step: a launch waits in the kernel for the flags of its
+predecessor on every rank (not for a completion event on its own GPU), and a one-CTA kernel after each launch
+publishes its completion.
 
 Only the linears and the gathers are in the step: attention, normalisation and residual adds of a
 real model are other kernels and are outside this path.  Each block reads the step's hidden state
@@ -90,7 +92,7 @@ class DecodeStack:
         self.bitmap = list(bitmap) if bitmap is not None else sample_bitmap(n_blocks, seed)
         if len(self.bitmap) != n_blocks:
             raise ValueError("bitmap length does not match the number of blocks")
-        if comm not in ("nccl", "p2p", "p2p_barrier"):
+        if comm not in ("nccl", "p2p", "p2p_barrier", "p2p_seq"):
             raise ValueError(comm)
         self.comm = comm if world > 1 else "nccl"
         self.blocks: List[_Block] = []
@@ -133,7 +135,7 @@ class DecodeStack:
         return total
 
     def launches_per_step(self) -> int:
-        return (8 if self.comm == "p2p_barrier" else 4) * self.n_blocks   # own kernels; NCCL's are not counted
+        return (8 if self.comm in ("p2p_barrier", "p2p_seq") else 4) * self.n_blocks   # own kernels; NCCL's are not counted
 
     # -------------------------------------------------------------- peer-mapped buffers for comm="p2p"
     def _setup_p2p(self, max_batch: int = 8):
@@ -155,7 +157,8 @@ class DecodeStack:
         from . import _C
         flags = [b + self._off["flags"] for b in self._peer_base]
         self._sync = _C.PeerSync(flags, self._symm[self._off["flags"]:self._off["flags"] + 256], self._epoch,
-                                 self._done, self._pstatus, self.rank) if self.comm == "p2p" else None
+                                 self._done, self._pstatus, self.rank, numbered=self.comm == "p2p_seq") \
+            if self.comm in ("p2p", "p2p_seq") else None
         self._local = {k: self._symm[o:] for k, o in self._off.items()}
         self._qkv_local = None
         torch.cuda.synchronize()
@@ -165,6 +168,11 @@ class DecodeStack:
         return self._local[name][: batch * width * 2].view(torch.float16).view(batch, width)
 
     def _barrier(self):
+        if self._sync is not None and self._sync.numbered:
+            from . import _C
+            _C.peer_publish(self._sync, self._seq)      # launch `seq` of the step is complete on this rank
+            self._seq += 1
+            return
         if self._sync is not None:
             return          # the decode kernels carry the hand-shake
         from . import _C
@@ -186,24 +194,28 @@ class DecodeStack:
         none = torch.empty(0, dtype=torch.float16, device=self.device)
         sk = lambda rows, k: _resolve(None, 1, B, rows, k, self.device, torch.float16, self.blocks[0].o.group_size)
         xq, xa, xm, xy = self._buf("q", B, d), self._buf("a", B, d), self._buf("m", B, f), self._buf("y", B, d)
+        self._seq = 0                    # numbered hand-shake: launches of the step in issue order
         for blk in self.blocks:
             w = blk.qkv
             _C.packed_gemv_scatter(x, w.packed, w.scales, w.zeros, none, self._qkv_local, peers("q"), dl, d, r * dl,
-                                   w.bits, d, w.group_size, sk(3 * dl, d), 1, 0, self._sync)
+                                   w.bits, d, w.group_size, sk(3 * dl, d), 1, 0, self._sync, self._seq)
             self._barrier()
             w = blk.o
             _C.packed_gemv_scatter(xq, w.packed, w.scales, w.zeros, none, self._o_local, peers("a"), dl, d, r * dl,
-                                   w.bits, d, w.group_size, sk(dl, d), 1, 0, self._sync)
+                                   w.bits, d, w.group_size, sk(dl, d), 1, 0, self._sync, self._seq)
             self._barrier()
             wg, wu = blk.gate, blk.up
             _C.fused_gate_up_scatter(xa, wg.packed, wg.scales, wg.zeros, wu.packed, wu.scales, wu.zeros, self._m_local,
-                                     peers("m"), fl, f, r * fl, wg.bits, d, wg.group_size, sk(2 * fl, d), 1, self._sync)
+                                     peers("m"), fl, f, r * fl, wg.bits, d, wg.group_size, sk(2 * fl, d), 1, self._sync,
+                                     self._seq)
             self._barrier()
             w = blk.down
             _C.packed_gemv_scatter(xm, w.packed, w.scales, w.zeros, none, self._o_local, peers("y"), dl, d, r * dl,
-                                   w.bits, f, w.group_size, sk(dl, f), 1, 0, self._sync)
+                                   w.bits, f, w.group_size, sk(dl, f), 1, 0, self._sync, self._seq)
             self._barrier()
-        if self._sync is not None:
+        if self._sync is not None and self._sync.numbered:
+            _C.peer_step_end(self._sync, self._seq)     # every rank has published the whole step; the base moves on
+        elif self._sync is not None:
             _C.peer_wait(self._sync)     # the peers' last slices have landed before anyone reads the result
         return xy
 

@@ -176,7 +176,7 @@ int run_decode(const char* who, const void* x, GemvParams& P, int bits, int64_t 
         default: rc = launch_gemv_generic_w4(dtype, x, G, rho, stream); break;
     }
     if (rc != CB_OK) return rc;
-    return sync ? launch_peer_signal(P, stream) : CB_OK;
+    return (sync && P.sync.on == 1) ? launch_peer_signal(P, stream) : CB_OK;
 }
 
 }  // namespace
@@ -277,8 +277,10 @@ static int fill_scatter(const char* who, GemvParams& P, const cb_scatter* sc, in
     }
     P.n_peers = sc->world; P.n_gather = (int)sc->n_gather; P.peer_ld = (int)sc->ld; P.peer_col = (int)sc->col;
     if (sc->sync) {
-        CB_REQUIRE(sc->my_flags && sc->epoch && sc->done && sc->status && sc->rank >= 0 && sc->rank < sc->world,
+        CB_REQUIRE(sc->sync == 1 || sc->sync == 2, "%s: scatter sync must be 0, 1 or 2", who);
+        CB_REQUIRE(sc->my_flags && sc->epoch && (sc->done || sc->sync == 2) && sc->status && sc->rank >= 0 && sc->rank < sc->world,
                    "%s: scatter hand-shake needs my_flags, epoch, done, status and a rank below world", who);
+        CB_REQUIRE(sc->sync == 1 || (sc->seq >= 0 && sc->seq < (1ll << 31)), "%s: scatter seq out of range", who);
         for (int i = 0; i < sc->world; ++i) {
             CB_REQUIRE(sc->peer_flags[i] != nullptr, "%s: peer %d has no flag array", who, i);
             P.sync.peer_flags[i] = reinterpret_cast<unsigned int*>(sc->peer_flags[i]);
@@ -288,7 +290,8 @@ static int fill_scatter(const char* who, GemvParams& P, const cb_scatter* sc, in
         P.sync.done = reinterpret_cast<int*>(sc->done);
         P.sync.status = sc->status;
         P.sync.rank = sc->rank;
-        P.sync.on = 1;
+        P.sync.on = sc->sync;
+        P.sync.seq = sc->sync == 2 ? (unsigned int)sc->seq : 0u;
     }
     return CB_OK;
 }

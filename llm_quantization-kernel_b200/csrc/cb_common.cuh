@@ -43,16 +43,23 @@ struct Proj {
     int n;
 };
 
-// Rank-to-rank hand-shake of a column-parallel stack, carried by the decode kernel itself: before it reads
-// its activations a launch waits until every peer has completed as many launches as this rank, and its last
-// CTA to finish tells every peer that one more launch is complete.
+// Rank-to-rank hand-shake of a column-parallel stack, carried by the decode kernel itself.
+// on == 1: before it reads its activations a launch waits until every peer has completed as many launches as this
+//          rank, and its last CTA to finish tells every peer that one more launch is complete.
+// on == 2: launches are numbered within a step (seq = 0, 1, ...).  Launch seq > 0 waits, before it reads its
+//          activations, until every rank (this one included) has published seq completed launches of the running step,
+//          i.e. flag >= *epoch + seq, where *epoch counts the launches of all finished steps and does not change while
+//          a step runs.  It publishes nothing itself: a one-CTA kernel after it does, once the launch has completed
+//          (cb_peer_publish), so the decode kernel neither fences nor counts its CTAs, and it does not wait for the
+//          completion event of its predecessor on this GPU either: the flags are the dependency.
 struct PeerSync {
     unsigned int* peer_flags[8];  // peer_flags[p] = rank p's flag array (one uint32 per rank), peer-mapped
     unsigned int* my_flags;       // this rank's own flag array: my_flags[p] = launches rank p has completed
-    unsigned int* epoch;          // launches this rank has completed
-    int* done;                    // CTAs of the running launch that are finished; zero between launches
+    unsigned int* epoch;          // on == 1: launches this rank has completed; on == 2: launches of all finished steps
+    int* done;                    // on == 1: CTAs of the running launch that are finished; zero between launches
     int* status;                  // 0, or 1 + the first peer that was not heard from in time
     int rank, on;
+    unsigned int seq;             // on == 2: number of this launch within its step
 };
 
 struct GemvParams {
@@ -81,10 +88,11 @@ constexpr long long kPeerWaitCycles = 2000000000ll;   // about a second
 // Returns (to thread 0) the number of launches this rank had completed, which peer_signal advances.
 __device__ __forceinline__ unsigned int peer_wait(const GemvParams& P) {
     if (!P.sync.on) return 0u;
+    if (P.sync.on == 2 && P.sync.seq == 0u) return 0u;      // the step's first launch reads the step's input
     const int p = threadIdx.x;
     unsigned int e = 0u;
     if (p < P.n_peers) {
-        e = *reinterpret_cast<volatile unsigned int*>(P.sync.epoch);
+        e = *reinterpret_cast<volatile unsigned int*>(P.sync.epoch) + (P.sync.on == 2 ? P.sync.seq : 0u);
         unsigned int seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(P.sync.my_flags + p) : "memory");
         if ((int)(seen - e) < 0 && *reinterpret_cast<volatile int*>(P.sync.status) == 0) {
@@ -106,7 +114,7 @@ __device__ __forceinline__ unsigned int peer_wait(const GemvParams& P) {
 // and the last CTA to arrive fences again before it advances this rank's launch count and publishes it: all
 // output stores of the grid (peer stores included) are visible to a peer that sees the new count.
 __device__ __forceinline__ void peer_signal(const GemvParams& P, unsigned int e) {
-    if (!P.sync.on) return;
+    if (P.sync.on != 1) return;
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence_system();

@@ -764,7 +764,9 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
     // no launch since the chain's last ordered one, and that was at most kMaxUnordered - 1 launches ago.
     ChainKey key{0ull, stream};
     cudaGraphNode_t tail = nullptr;
-    const bool in_chain = pdl && chains && capture_tail(stream, &key.capture, &tail);
+    // A launch of a numbered hand-shake (sync.on == 2) takes no part in chains: its dependency is the ranks' flags.
+    const bool numbered = P.sync.on == 2;
+    const bool in_chain = !numbered && pdl && chains && capture_tail(stream, &key.capture, &tail);
     std::unique_lock<std::mutex> lock(g_chain_mutex, std::defer_lock);
     LaunchRec rec{};
     S.launch_kind = kLaunchPlain;
@@ -791,6 +793,14 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
         ++g_chain_counts[follower ? 1 : 0];
         if (follower) ++g_chain_counts[free_run ? 3 : 2];
     }
+    // Numbered hand-shake: launch seq > 0 starts as soon as its predecessor lets it, never waits for that predecessor's
+    // completion (it waits for the flags instead) and keeps the completion order like any free launch; launch 0 of a
+    // step is an ordinary fully serialised launch, so that nothing of the step starts before the previous step's end.
+    bool programmatic = pdl;
+    if (numbered) {
+        S.launch_kind = (P.sync.seq > 0u && pdl) ? kLaunchFree : kLaunchPlain;
+        if (P.sync.seq == 0u) programmatic = false;
+    }
     // Which build of the kernel.  A FREE single-pass launch of at most a third of an SM's shared memory runs the build
     // capped at 80 registers, so that three consecutive launches of the chain are resident per SM (measured at
     // 4096x4096, independent launches: W4 2.80 -> 2.57 us, W3 3.08 -> 2.91, W2 2.61 -> 2.23); so does a plan that puts
@@ -799,7 +809,7 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
     using Kern = void (*)(const unsigned char*, const StreamParams);
     Kern kern = gemv_stream_kernel<BITS, KIND, 2>;
     int which = 0;
-    if ((S.launch_kind == kLaunchFree && pick.npass == 1 && smem <= kSmemCapThree) || pick.three) {
+    if ((S.launch_kind == kLaunchFree && !numbered && pick.npass == 1 && smem <= kSmemCapThree) || pick.three) {
         kern = gemv_stream_kernel<BITS, KIND, 3>;
         which = 1;
     }
@@ -823,7 +833,7 @@ int launch_t(const void* x, GemvParams P, int64_t rho, bool pdl, bool chains, vo
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = programmatic ? 1 : 0;
     CB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, reinterpret_cast<const unsigned char*>(x), S));
     if (in_chain) {
         unsigned long long id = 0;

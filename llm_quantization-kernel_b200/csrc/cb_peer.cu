@@ -48,6 +48,43 @@ __global__ void peer_barrier_kernel(const PeerBarrierParams P) {
     if (p == 0) *P.epoch = e;
 }
 
+// Numbered hand-shake (PeerSync::on == 2).  After decode launch `seq` of a step this kernel tells every rank, this one
+// included, that the launch is complete: it is resident before the decode launch ends (programmatic dependent), its
+// griddepcontrol.wait returns when that launch has completed and its stores -- the peer stores too -- are visible,
+// and a release store at system scope then carries the count epoch + seq + 1 to every rank's flag array.  It lets its
+// own successor, the next decode launch, start at once.
+__global__ void peer_publish_kernel(const PeerBarrierParams P, const unsigned int seq) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int p = threadIdx.x;
+    if (p < P.world) {
+        const unsigned int e = *reinterpret_cast<volatile unsigned int*>(P.epoch) + seq + 1u;
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.peer_flags[p] + P.rank), "r"(e) : "memory");
+    }
+}
+
+// End of a step of `launches` numbered launches: waits (bounded) until every rank has published all of them -- the
+// gathered result is then complete on this rank and no peer still reads or writes a buffer of the step -- and only
+// then advances the step base.  An ordinary launch, and the step's first decode launch after it is one too, so the
+// next step reads the new base.
+__global__ void peer_step_end_kernel(const PeerBarrierParams P, const unsigned int launches) {
+    const int p = threadIdx.x;
+    const unsigned int e = *reinterpret_cast<volatile unsigned int*>(P.epoch) + launches;
+    if (p < P.world && *reinterpret_cast<volatile int*>(P.status) == 0) {
+        const long long t0 = clock64();
+        unsigned int seen = 0;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(P.my_flags + p) : "memory");
+            if ((int)(seen - e) >= 0) break;
+            if (clock64() - t0 > kPeerWaitCycles) { atomicCAS(P.status, 0, 1 + p); break; }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    if (p == 0) *P.epoch = e;
+}
+
 // The two halves of the in-kernel hand-shake as kernels of their own, for decode kernels that do not carry it.
 __global__ void peer_wait_kernel(const GemvParams P) { peer_wait(P); }
 __global__ void peer_signal_kernel(const GemvParams P) {
@@ -94,6 +131,54 @@ extern "C" int cb_peer_barrier(void* const* peer_flags, void* my_flags, void* ep
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 1 : 0;
     CB_CUDA_TRY(cudaLaunchKernelEx(&cfg, peer_barrier_kernel, P));
+    return CB_OK;
+}
+
+namespace {
+int barrier_params(const char* who, const cb_scatter* sc, cb::PeerBarrierParams& P) {
+    using namespace cb;
+    if (sc == nullptr || sc->sync != 2 || sc->world < 1 || sc->world > 8 || sc->rank < 0 || sc->rank >= sc->world ||
+        !sc->my_flags || !sc->epoch || !sc->status) {
+        set_error("%s: needs a scatter description of a numbered hand-shake (sync == 2) with my_flags, epoch and status", who);
+        return CB_ERR_INVALID;
+    }
+    for (int i = 0; i < sc->world; ++i) {
+        if (sc->peer_flags[i] == nullptr) { set_error("%s: peer %d has no flag array", who, i); return CB_ERR_INVALID; }
+        P.peer_flags[i] = reinterpret_cast<unsigned int*>(sc->peer_flags[i]);
+    }
+    P.my_flags = reinterpret_cast<unsigned int*>(sc->my_flags);
+    P.epoch = reinterpret_cast<unsigned int*>(sc->epoch);
+    P.status = sc->status;
+    P.world = sc->world; P.rank = sc->rank;
+    return CB_OK;
+}
+}  // namespace
+
+extern "C" int cb_peer_publish(const cb_scatter* sc, void* stream) {
+    using namespace cb;
+    PeerBarrierParams P{};
+    const int rc = barrier_params("peer_publish", sc, P);
+    if (rc != CB_OK) return rc;
+    if (sc->seq < 0 || sc->seq >= (1ll << 31)) { set_error("peer_publish: seq out of range"); return CB_ERR_INVALID; }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1); cfg.blockDim = dim3(32); cfg.dynamicSmemBytes = 0;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    CB_CUDA_TRY(cudaLaunchKernelEx(&cfg, peer_publish_kernel, P, (unsigned int)sc->seq));
+    return CB_OK;
+}
+
+extern "C" int cb_peer_step_end(const cb_scatter* sc, int64_t launches, void* stream) {
+    using namespace cb;
+    PeerBarrierParams P{};
+    const int rc = barrier_params("peer_step_end", sc, P);
+    if (rc != CB_OK) return rc;
+    if (launches < 1 || launches >= (1ll << 31)) { set_error("peer_step_end: launches out of range"); return CB_ERR_INVALID; }
+    peer_step_end_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(P, (unsigned int)launches);
+    CB_CUDA_TRY(cudaGetLastError());
     return CB_OK;
 }
 

@@ -18,7 +18,7 @@ def main():
     from crispybits_kernels.stack import DecodeStack
     kw = dict(n_blocks=3, d_model=1024, d_ff=2048, bitmap=[4, 2, 3], device=dev, std=0.05)
     one = DecodeStack(rank=0, world=1, **kw)
-    stacks = {c: DecodeStack(rank=rank, world=world, comm=c, **kw) for c in ("nccl", "p2p", "p2p_barrier")}
+    stacks = {c: DecodeStack(rank=rank, world=world, comm=c, **kw) for c in ("nccl", "p2p", "p2p_barrier", "p2p_seq")}
     g = torch.Generator().manual_seed(5)
     for B in (1, 3, 8):
         for it in range(4):
@@ -26,7 +26,7 @@ def main():
             ref = one.step(x).float()
             y = {c: s.step(x).clone() for c, s in stacks.items()}
             torch.cuda.synchronize()
-            for c in ("p2p", "p2p_barrier"):
+            for c in ("p2p", "p2p_barrier", "p2p_seq"):
                 assert torch.equal(y[c], y["nccl"]), (c, B, it)
                 assert stacks[c].peer_status() == 0, (c, stacks[c].peer_status())
             err = ((y["nccl"].float() - ref).abs().max() / ref.abs().max()).item()
@@ -34,7 +34,7 @@ def main():
     # graph replays keep the launch counts going
     x = torch.randn(2, 1024, generator=g).half().to(dev)
     want = stacks["nccl"].step(x).clone()
-    for c in ("p2p", "p2p_barrier"):
+    for c in ("p2p", "p2p_barrier", "p2p_seq"):
         st = stacks[c]
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream())
