@@ -55,6 +55,11 @@ template <int KIND> struct FragKind {
     __device__ static __forceinline__ constexpr uint32_t pow2neg(int e) {
         return kBf ? (uint32_t)(((127 - e) << 7) * 0x10001u) : (uint32_t)(((15 - e) << 10) * 0x10001u);
     }
+    // (2^-lo, 2^-hi) in the operand type: low half first
+    __device__ static __forceinline__ constexpr uint32_t pow2neg2(int lo, int hi) {
+        return kBf ? (uint32_t)((127 - lo) << 7) | ((uint32_t)((127 - hi) << 7) << 16)
+                   : (uint32_t)((15 - lo) << 10) | ((uint32_t)((15 - hi) << 10) << 16);
+    }
     __device__ static __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
         uint32_t r;
         if constexpr (kBf) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -68,8 +73,10 @@ template <int BITS, int KIND> struct Frag;
 template <int KIND> struct Frag<4, KIND> : FragKind<KIND> {
     using F = FragKind<KIND>;
     __device__ static __forceinline__ constexpr int pair_lo(int m) { return 8 * (m >> 2) + (m & 3); }   // word i: e[4i+j] = (8i+j, 8i+j+4)
-    __device__ static __forceinline__ constexpr int pair_gap() { return 4; }
+    __device__ static __forceinline__ constexpr int pair_hi(int m) { return pair_lo(m) + 4; }
     __device__ static __forceinline__ constexpr int shift(int m) { return F::kBf ? 0 : ((m & 1) ? 4 : 0); }
+    // what the activations of pair m are multiplied by when they are staged: (2^-p, 2^-p') for fields at bits p, 16 + p'
+    __device__ static __forceinline__ constexpr uint32_t scale2(int m) { return F::pow2neg2(shift(m), shift(m)); }
     __device__ static __forceinline__ void run(const uint32_t (&w)[4], uint32_t (&e)[16]) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -90,11 +97,12 @@ template <int KIND> struct Frag<4, KIND> : FragKind<KIND> {
 template <int KIND> struct Frag<2, KIND> : FragKind<KIND> {
     using F = FragKind<KIND>;
     __device__ static __forceinline__ constexpr int pair_lo(int m) { return 16 * (m >> 3) + (m & 7); }  // word i: e[8i+j] = (16i+j, 16i+j+8)
-    __device__ static __forceinline__ constexpr int pair_gap() { return 8; }
+    __device__ static __forceinline__ constexpr int pair_hi(int m) { return pair_lo(m) + 8; }
     __device__ static __forceinline__ constexpr int shift(int m) {
         const int j = m & 7;
         return F::kBf ? 2 * (j % 3) : (j < 5 ? 2 * j : 2 * (j - 5));
     }
+    __device__ static __forceinline__ constexpr uint32_t scale2(int m) { return F::pow2neg2(shift(m), shift(m)); }
     __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t (&e)[16]) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -124,16 +132,42 @@ template <int KIND> struct Frag<2, KIND> : FragKind<KIND> {
 };
 
 template <int KIND> struct Frag<3, KIND> : FragKind<KIND> {
-    // e[j] = (code j, code j+16): the chunk is a 96-bit stream; code j sits at bit 3j, code j+16 at bit 3j+48.
-    // Windows of 15 bits (5 codes) of both halves are brought side by side into one register with funnel shifts
-    // (which also reassemble the codes that straddle a word) and a byte permute.
+    // The chunk is a 96-bit stream with code j at bit 3j.
+    //
+    // fp16 subnormal operands (KIND 0).  A field may sit anywhere in bits 0..10 of its half (values with exponent field
+    // 0 or 1 are linear in the bit pattern), and the two codes of a register need not be 16 positions apart: the
+    // activations are arranged to match.  So six windows of the stream -- one word as it is, three funnel shifts, two
+    // shifts -- hold all 32 codes with three (two) low-half and three (two) high-half fields each, and 16 ANDs finish:
+    //   w0               codes (0,6) (1,7) (2,8)          low fields at bits 0, 3, 6; high fields at 16 + 2, 5, 8
+    //   stream >> 9      codes (3,9) (4,10) (5,11)        the same masks
+    //   stream >> 36     codes (12,18) (13,19) (14,20)
+    //   stream >> 45     codes (15,21) (16,22) (17,23)
+    //   w2 >> 4          codes (24,28) (25,29)            low fields at bits 4, 7; high fields at 16 + 0, 3
+    //   w2 >> 10         codes (26,30) (27,31)
+    // 21 integer instructions per 32 codes.
+    //
+    // Offset operands (KIND 1, 2).  e[j] = (code j, code j+16): windows of 15 bits (5 codes) of both halves are brought
+    // side by side into one register with funnel shifts (which also reassemble the codes that straddle a word) and a
+    // byte permute; fields stay inside the mantissa of the offset.  30 instructions per 32 codes.
     using F = FragKind<KIND>;
-    __device__ static __forceinline__ constexpr int pair_lo(int m) { return m; }
-    __device__ static __forceinline__ constexpr int pair_gap() { return 16; }
+    static constexpr bool kWindows = KIND == kFragSubnormal;
+    __device__ static __forceinline__ constexpr int pair_lo(int m) {
+        if (!kWindows) return m;
+        return m < 12 ? 12 * (m / 6) + (m % 6) : 24 + (m - 12);           // 0..5, 12..17, 24..27
+    }
+    __device__ static __forceinline__ constexpr int pair_hi(int m) {
+        if (!kWindows) return m + 16;
+        return m < 12 ? pair_lo(m) + 6 : pair_lo(m) + 4;
+    }
     __device__ static __forceinline__ constexpr int shift(int m) {
         if (m == 15) return 0;
         const int j = m % 5;
         return F::kBf ? 3 * (j & 1) : (j < 3 ? 3 * j : 3 * (j - 3));
+    }
+    __device__ static __forceinline__ constexpr uint32_t scale2(int m) {
+        if (!kWindows) return F::pow2neg2(shift(m), shift(m));
+        if (m < 12) return F::pow2neg2(3 * (m % 3), 2 + 3 * (m % 3));
+        return (m & 1) ? F::pow2neg2(7, 3) : F::pow2neg2(4, 0);
     }
     __device__ static __forceinline__ void five(uint32_t p, uint32_t* e) {
         if constexpr (F::kBf) {
@@ -153,14 +187,30 @@ template <int KIND> struct Frag<3, KIND> : FragKind<KIND> {
         }
     }
     __device__ static __forceinline__ void run(const uint32_t (&w)[3], uint32_t (&e)[16]) {
-        // stream bits [s, s+16) of the first half next to bits [48+s, 48+s+16) of the second half
-        const uint32_t l1 = __funnelshift_r(w[0], w[1], 15), l2 = __funnelshift_r(w[0], w[1], 30);
-        const uint32_t u0 = __funnelshift_r(w[1], w[2], 16), u1 = __funnelshift_r(w[1], w[2], 31), u2 = w[2] >> 14;
-        five(__byte_perm(w[0], u0, 0x5410), e);
-        five(__byte_perm(l1, u1, 0x5410), e + 5);
-        five(__byte_perm(l2, u2, 0x5410), e + 10);
-        const uint32_t last = __byte_perm(w[1] >> 13, w[2] >> 29, 0x5410);               // codes 15 and 31
-        e[15] = F::field(last, 0x00070007u);
+        if constexpr (kWindows) {
+            const uint32_t win[4] = {w[0], __funnelshift_r(w[0], w[1], 9), __funnelshift_r(w[1], w[2], 4),
+                                     __funnelshift_r(w[1], w[2], 13)};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                e[3 * i + 0] = win[i] & 0x001C0007u;
+                e[3 * i + 1] = win[i] & 0x00E00038u;
+                e[3 * i + 2] = win[i] & 0x070001C0u;
+            }
+            const uint32_t t4 = w[2] >> 4, t10 = w[2] >> 10;
+            e[12] = t4 & 0x00070070u;
+            e[13] = t4 & 0x00380380u;
+            e[14] = t10 & 0x00070070u;
+            e[15] = t10 & 0x00380380u;
+        } else {
+            // stream bits [s, s+16) of the first half next to bits [48+s, 48+s+16) of the second half
+            const uint32_t l1 = __funnelshift_r(w[0], w[1], 15), l2 = __funnelshift_r(w[0], w[1], 30);
+            const uint32_t u0 = __funnelshift_r(w[1], w[2], 16), u1 = __funnelshift_r(w[1], w[2], 31), u2 = w[2] >> 14;
+            five(__byte_perm(w[0], u0, 0x5410), e);
+            five(__byte_perm(l1, u1, 0x5410), e + 5);
+            five(__byte_perm(l2, u2, 0x5410), e + 10);
+            const uint32_t last = __byte_perm(w[1] >> 13, w[2] >> 29, 0x5410);               // codes 15 and 31
+            e[15] = F::field(last, 0x00070007u);
+        }
     }
 };
 

@@ -294,9 +294,9 @@ gemv_stream_kernel(const unsigned char* x, const StreamParams S) {
             uint32_t xf[16];
 #pragma unroll
             for (int m = 0; m < 16; ++m) {
-                const int lo = F::pair_lo(m), hi = lo + F::pair_gap();
+                const int lo = F::pair_lo(m), hi = F::pair_hi(m);          // same parity: one permute pairs them
                 xf[m] = __byte_perm(raw[lo >> 1], raw[hi >> 1], (lo & 1) ? 0x7632 : 0x5410);
-                if (F::shift(m) != 0) xf[m] = F::mul2(xf[m], F::pow2neg(F::shift(m)));
+                if (F::scale2(m) != F::pow2neg2(0, 0)) xf[m] = F::mul2(xf[m], F::scale2(m));
             }
             if (on) {
                 const uint32_t dst = s_xs + (uint32_t)(((gl * P.B + b) * 4 + tq) * 16);
