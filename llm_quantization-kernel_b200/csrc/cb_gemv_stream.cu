@@ -576,7 +576,7 @@ struct LaunchRec {
     bool scratch;          // Split-K partial sums and counters
     bool exclusive;        // rank hand-shake or peer stores: ordered after everything, and everything after it
 };
-constexpr int kMaxUnordered = 32;    // launches a chain may run without an ordered one in between
+constexpr int kMaxUnordered = 64;    // launches a chain may run without an ordered one in between
 struct ChainState {
     cudaGraphNode_t last;              // the node of this library's latest launch on (capture, stream)
     int count;                         // launches since (and including) the last ordered one
