@@ -7,8 +7,9 @@
 // (3) the stretch between "the activations exist" and "the outputs are stored" must be as short as possible.
 //
 //  (1) Each CTA owns a contiguous slab of virtual output rows and one of split_k K-partitions.  Rows of a slab are
-//      fetched 32 (or 16) at a time ("a pass") with one cp.async.bulk per row into a shared-memory ring guarded by
-//      mbarriers; scales and zeros follow as 4-byte cp.async issued by all threads.  The copies of the first passes
+//      fetched up to 32 at a time ("a pass") with one cp.async.bulk per row into a shared-memory ring guarded by
+//      mbarriers; scales and zeros follow as 4-byte cp.async issued by all threads.  Where the matrix allows it every
+//      CTA has a single pass and one, two or three CTAs share an SM (plan_stream).  The copies of the first passes
 //      are issued before anything else, also before the kernel waits for its predecessor in the stream, so they
 //      overlap the previous kernel.  Packed weights are assumed constant for the duration of the call.
 //  (2) The 8 warps split the K-partition by quantisation group.  A packed word becomes MMA A operands with one
@@ -16,9 +17,10 @@
 //      number, code * 2^(p-24) for a field at bit p, and the activations that meet it are multiplied by 2^-p when
 //      they are staged, once per CTA, in the order the unpack produces codes.  mma.sync m16n8k16 (16 weight rows x
 //      16 codes, up to 8 batch rows as the B operand, fp32 accumulation) then gives 2^-24 * sum(q x) per group; the
-//      zero point enters as  -z * sum(x)  through the accumulator's initial value, the scale as one FMA per group:
-//      acc += s * (sum(q x) - z sum(x))   (Crispybits/Kernel/csrc/packed_gemv.cu:131-135).  The group sums of x come
-//      from eight more MMAs per 8 (group, batch row) pairs with an all-ones A operand.  bf16 has too few mantissa
+//      scale enters as one FMA per group, acc += s * sum(q x), and the zero-point terms  s * z * sum(x)  of a pass are
+//      added up once per pass with lane = row and subtracted in the final reduction:
+//      y = sum over groups of  s * (sum(q x) - z sum(x))   (Crispybits/Kernel/csrc/packed_gemv.cu:131-135).  The group
+//      sums of x come from eight more MMAs per 8 (group, batch row) pairs with an all-ones A operand.  bf16 has too few mantissa
 //      bits and too small an exponent range for the subnormal form: there (field | 0x4300) = 128 + code is used and
 //      the 128 * sum(x') it adds is subtracted with the zero-point term.
 //  (3) Hand-over.  A launch is a programmatic dependent launch: it may start (and prefetch weights) while its
@@ -36,7 +38,10 @@
 //          predecessors; only its first CTA waits for the predecessor's completion before it EXITS, so grids still
 //          complete in launch order and whatever follows the chain sees all of it.
 //      No device-side state is involved.  Outside capture every launch waits at once and triggers at once, as a plain
-//      programmatic dependent launch does.
+//      programmatic dependent launch does.  Free single-pass launches run a build of the kernel capped at 80 registers,
+//      so that three launches of a chain fit an SM: independent launches then complete every (CTA lifetime) / 3.
+//      In a column-parallel stack with the numbered hand-shake (PeerSync::on == 2) a launch is free in this sense too:
+//      its dependency is the ranks' flags, which it polls before it reads x.
 //
 // The dot product is permutation-invariant, so the order in which codes meet MMA k-slots is chosen to suit the unpack.
 #include <algorithm>
