@@ -79,6 +79,7 @@ typedef struct cb_scatter {
     void* done;
     int* status;
     int64_t seq;
+    int64_t need;
 } cb_scatter;
 
 /* Message of the last error raised on this thread ("" if none). */
@@ -148,9 +149,11 @@ int cb_peer_wait(const cb_scatter* scatter, void* stream);
 
 /* Numbered hand-shake (scatter->sync == 2), the cheapest of the three: the launches of a step are numbered seq = 0,
  * 1, ... in issue order, identically on every rank.  A scatter launch with seq > 0 waits in the kernel (bounded) until
- * every rank has published seq completed launches of the running step (flag >= *epoch + seq; `epoch`, a zeroed uint32
- * in this rank's memory, counts the launches of all finished steps) and does not wait for its predecessor's completion
- * on this GPU; the launch with seq == 0 is an ordinary serialised launch and reads the step's input.  After EVERY
+ * every rank has published `need` completed launches of the running step (flag >= *epoch + need; `epoch`, a zeroed
+ * uint32 in this rank's memory, counts the launches of all finished steps) and does not wait for its predecessor's
+ * completion on this GPU; the launch with seq == 0 is an ordinary serialised launch and reads the step's input.  `need`
+ * is seq for a launch that reads what launch seq - 1 gathered; a launch that reads older data may pass less, but never
+ * less than 1 + the number of the last launch that read, on any rank, a buffer this launch overwrites (need <= seq).  After EVERY
  * scatter launch call cb_peer_publish with the same seq: a one-CTA kernel that is released by the launch's completion
  * and stores *epoch + seq + 1 into every rank's flag array.  After the step's last publish call cb_peer_step_end with
  * the number of launches: it waits (bounded) until every rank has published all of them -- the result is then

@@ -345,7 +345,7 @@ class _Scatter(ctypes.Structure):
     """struct cb_scatter of include/crispybits_b200.h"""
     _fields_ = [("peer_out", _vp * 8), ("world", _int), ("n_gather", _i64), ("ld", _i64), ("col", _i64),
                 ("sync", _int), ("rank", _int), ("peer_flags", _vp * 8), ("my_flags", _vp), ("epoch", _vp),
-                ("done", _vp), ("status", _vp), ("seq", _i64)]
+                ("done", _vp), ("status", _vp), ("seq", _i64), ("need", _i64)]
 
 
 class PeerSync:
@@ -371,13 +371,15 @@ for _f in ("cb_packed_gemv_scatter", "cb_fused_gate_up_scatter", "cb_peer_barrie
     getattr(_lib, _f).restype = _int
 
 
-def _scatter(peer_ptrs, n_gather: int, ld: int, col: int, sync: "PeerSync | None" = None, seq: int = 0) -> _Scatter:
+def _scatter(peer_ptrs, n_gather: int, ld: int, col: int, sync: "PeerSync | None" = None, seq: int = 0,
+             need: "int | None" = None) -> _Scatter:
     sc = _Scatter()
     for i, ptr in enumerate(peer_ptrs):
         sc.peer_out[i] = ptr
     sc.world, sc.n_gather, sc.ld, sc.col = len(peer_ptrs), n_gather, ld, col
     if sync is not None:
         sc.sync, sc.rank, sc.seq = (2 if sync.numbered else 1), sync.rank, int(seq)
+        sc.need = int(seq) if need is None else int(need)
         for i, ptr in enumerate(sync.peer_flag_ptrs):
             sc.peer_flags[i] = ptr
         sc.my_flags, sc.epoch = sync.my_flags.data_ptr(), sync.epoch.data_ptr()
@@ -386,7 +388,7 @@ def _scatter(peer_ptrs, n_gather: int, ld: int, col: int, sync: "PeerSync | None
 
 
 def packed_gemv_scatter(x, packed, scales, zeros, bias, out, peer_ptrs, n_gather, ld, col, bits, in_features,
-                        group_size, split_k, rho, act, sync=None, seq=0):
+                        group_size, split_k, rho, act, sync=None, seq=0, need=None):
     """packed_gemv whose output rows < n_gather go to every rank's gathered buffer (peer pointers) at column
     `col` of a [B, ld] matrix; the other rows go to `out` [B, N].  `seq`: number of the launch within its step, for a
     numbered hand-shake."""
@@ -401,7 +403,7 @@ def packed_gemv_scatter(x, packed, scales, zeros, bias, out, peer_ptrs, n_gather
         st = _stream(x)
         pk = max(1, min(split_k, -(-k // 32)))
         sc = _decode_scratch(x, st, B, n, pk)
-        w, s = _weight(packed, scales, zeros, bias), _scatter(peer_ptrs, int(n_gather), int(ld), int(col), sync, seq)
+        w, s = _weight(packed, scales, zeros, bias), _scatter(peer_ptrs, int(n_gather), int(ld), int(col), sync, seq, need)
         _rc(_lib.cb_packed_gemv_scatter(x.data_ptr(), B, ctypes.byref(w), out.data_ptr(), ctypes.byref(s), k, bits, gs,
                                         _DTYPE[x.dtype], pk, int(rho), int(act), _ptr(sc), 0 if sc is None else sc.numel(), st))
     return out

@@ -197,8 +197,12 @@ class DecodeStack:
         self._seq = 0                    # numbered hand-shake: launches of the step in issue order
         for blk in self.blocks:
             w = blk.qkv
+            # QKV reads the step's input, not what the previous launch gathered: it only has to know that nobody still
+            # reads the Q buffer it overwrites (the previous block's o_proj, three launches back), which the launch
+            # before it has already waited for -- so it asks for one launch less and overlaps that launch's hand-shake
             _C.packed_gemv_scatter(x, w.packed, w.scales, w.zeros, none, self._qkv_local, peers("q"), dl, d, r * dl,
-                                   w.bits, d, w.group_size, sk(3 * dl, d), 1, 0, self._sync, self._seq)
+                                   w.bits, d, w.group_size, sk(3 * dl, d), 1, 0, self._sync, self._seq,
+                                   max(0, self._seq - 1))
             self._barrier()
             w = blk.o
             _C.packed_gemv_scatter(xq, w.packed, w.scales, w.zeros, none, self._o_local, peers("a"), dl, d, r * dl,

@@ -281,6 +281,7 @@ static int fill_scatter(const char* who, GemvParams& P, const cb_scatter* sc, in
         CB_REQUIRE(sc->my_flags && sc->epoch && (sc->done || sc->sync == 2) && sc->status && sc->rank >= 0 && sc->rank < sc->world,
                    "%s: scatter hand-shake needs my_flags, epoch, done, status and a rank below world", who);
         CB_REQUIRE(sc->sync == 1 || (sc->seq >= 0 && sc->seq < (1ll << 31)), "%s: scatter seq out of range", who);
+        CB_REQUIRE(sc->sync == 1 || (sc->need >= 0 && sc->need <= sc->seq), "%s: scatter need must be 0..seq", who);
         for (int i = 0; i < sc->world; ++i) {
             CB_REQUIRE(sc->peer_flags[i] != nullptr, "%s: peer %d has no flag array", who, i);
             P.sync.peer_flags[i] = reinterpret_cast<unsigned int*>(sc->peer_flags[i]);
@@ -292,6 +293,7 @@ static int fill_scatter(const char* who, GemvParams& P, const cb_scatter* sc, in
         P.sync.rank = sc->rank;
         P.sync.on = sc->sync;
         P.sync.seq = sc->sync == 2 ? (unsigned int)sc->seq : 0u;
+        P.sync.need = sc->sync == 2 ? (unsigned int)sc->need : 0u;
     }
     return CB_OK;
 }

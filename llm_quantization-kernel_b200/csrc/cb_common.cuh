@@ -60,6 +60,9 @@ struct PeerSync {
     int* status;                  // 0, or 1 + the first peer that was not heard from in time
     int rank, on;
     unsigned int seq;             // on == 2: number of this launch within its step
+    unsigned int need;            // on == 2: launches of the step that every rank must have published before this one
+                                  //          reads its activations (seq for a launch that consumes its predecessor's
+                                  //          output; less for one that does not)
 };
 
 struct GemvParams {
@@ -88,11 +91,11 @@ constexpr long long kPeerWaitCycles = 2000000000ll;   // about a second
 // Returns (to thread 0) the number of launches this rank had completed, which peer_signal advances.
 __device__ __forceinline__ unsigned int peer_wait(const GemvParams& P) {
     if (!P.sync.on) return 0u;
-    if (P.sync.on == 2 && P.sync.seq == 0u) return 0u;      // the step's first launch reads the step's input
+    if (P.sync.on == 2 && P.sync.need == 0u) return 0u;     // nothing of this step has to be complete yet
     const int p = threadIdx.x;
     unsigned int e = 0u;
     if (p < P.n_peers) {
-        e = *reinterpret_cast<volatile unsigned int*>(P.sync.epoch) + (P.sync.on == 2 ? P.sync.seq : 0u);
+        e = *reinterpret_cast<volatile unsigned int*>(P.sync.epoch) + (P.sync.on == 2 ? P.sync.need : 0u);
         unsigned int seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(P.sync.my_flags + p) : "memory");
         if ((int)(seen - e) < 0 && *reinterpret_cast<volatile int*>(P.sync.status) == 0) {
