@@ -62,7 +62,8 @@ COMM_TEXT = {
                    "one-CTA flag barrier kernel (programmatic dependent launch) after each launch",
     "p2p_seq": "all-gather fused into the decode kernel's epilogue as peer stores over NVLink; launches numbered within "
                "the step, each waits in the kernel for its predecessor's flag from every rank (no completion event on its "
-               "own GPU), a one-CTA kernel after each launch publishes its completion",
+               "own GPU; a block's QKV launch, which reads the step's input, for the one before that), a one-CTA kernel after "
+               "each launch publishes its completion",
 }
 METRIC_STACK = "packed mixed-precision decode stack effective HBM bandwidth (Llama-2-7B shapes, 32 blocks)"
 # dram__bytes_read + dram__bytes_write per W4 4096x4096 launch, from the ncu capture summarised under profiles/

@@ -19,7 +19,8 @@ it reads its activations and publishes its completion to them, so a block is fou
 else; `comm="p2p_barrier"` keeps the stores but separates the hand-shake into a one-CTA barrier kernel
 after each launch; `comm="p2p_seq"` numbers the launches of a step: a launch waits in the kernel for the flags of its
 predecessor on every rank (not for a completion event on its own GPU), and a one-CTA kernel after each launch
-publishes its completion.
+publishes its completion; a block's QKV launch, which reads x and not the previous block's output, waits for one
+launch less and so overlaps the previous hand-shake.
 
 Only the linears and the gathers are in the step: attention, normalisation and residual adds of a
 real model are other kernels and are outside this path.  Each block reads the step's hidden state
