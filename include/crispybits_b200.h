@@ -153,9 +153,9 @@ int cb_peer_wait(const cb_scatter* scatter, void* stream);
  * uint32 in this rank's memory, counts the launches of all finished steps) and does not wait for its predecessor's
  * completion on this GPU; the launch with seq == 0 is an ordinary serialised launch and reads the step's input.  `need`
  * is seq for a launch that reads what launch seq - 1 gathered; a launch that reads older data may pass less, but never
- * less than 1 + the number of the last launch that read, on any rank, a buffer this launch overwrites (need <= seq).  After EVERY
- * scatter launch call cb_peer_publish with the same seq: a one-CTA kernel that is released by the launch's completion
- * and stores *epoch + seq + 1 into every rank's flag array.  After the step's last publish call cb_peer_step_end with
+ * less than 1 + the number of the last launch that read, on any rank, a buffer this launch overwrites (need <= seq).
+ * After EVERY scatter launch call cb_peer_publish with the same seq: a one-CTA kernel that is released by the launch's
+ * completion and stores *epoch + seq + 1 into every rank's flag array.  After the step's last publish call cb_peer_step_end with
  * the number of launches: it waits (bounded) until every rank has published all of them -- the result is then
  * complete here and no peer touches the step's buffers any more -- and advances *epoch.  `done` is not used.  Buffers
  * may be reused as with sync == 1.  New for the multi-GPU stack. */
