@@ -75,3 +75,38 @@ def test_decode_plan_is_host_arithmetic_and_stays_inside_an_sm():
     # outside the kernel's domain: K not a multiple of 256, batch above 8
     assert lib.cb_decode_plan(4, 1, 4096, 4096 + 128, 1, 1, 148, out) != 0
     assert lib.cb_decode_plan(4, 9, 4096, 4096, 1, 1, 148, out) != 0
+
+
+def test_python_struct_mirrors_match_the_c_header(tmp_path):
+    """The ctypes mirrors in crispybits_kernels/_C.py lay cb_weight and cb_scatter out exactly as a C compiler lays out
+    the header's declarations (size and the offset of every field)."""
+    import subprocess
+    import sys
+
+    sys.path.insert(0, PKG)
+    from crispybits_kernels import _C
+
+    mirrors = {"cb_weight": _C._Weight, "cb_scatter": _C._Scatter}
+    lines = []
+    for cname, cls in mirrors.items():
+        lines.append(f'printf("{cname} %zu\\n", sizeof({cname}));')
+        for field, _ in cls._fields_:
+            lines.append(f'printf("{cname}.{field} %zu\\n", offsetof({cname}, {field}));')
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "crispybits_b200.h"\nint main(void) {\n'
+                   + "\n".join(lines) + "\nreturn 0; }\n")
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    got = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True,
+                                                       text=True).stdout.splitlines())
+    for cname, cls in mirrors.items():
+        assert int(got[cname]) == ctypes.sizeof(cls), cname
+        for field, _ in cls._fields_:
+            assert int(got[f"{cname}.{field}"]) == getattr(cls, field).offset, (cname, field)
+    # and the header declares no field that the mirror lacks
+    text = open(os.path.join(ROOT, "include", "crispybits_b200.h")).read()
+    for cname, cls in mirrors.items():
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        declared = re.findall(r"(\w+)(?:\[\d+\])?\s*;", body)
+        assert declared == [f for f, _ in cls._fields_], cname
